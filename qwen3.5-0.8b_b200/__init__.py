@@ -1,0 +1,3 @@
+"""B200-native decode path of the Qwen3.5-0.8B text tower: host-side mirror of the
+reference engine's step/state/prefill/MTP interface over a C-ABI CUDA library."""
+from . import weights  # noqa: F401
