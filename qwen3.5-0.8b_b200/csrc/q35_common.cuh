@@ -1,0 +1,134 @@
+// Shared device helpers and launcher declarations for the sm_100a decode-path kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace q35 {
+
+constexpr int kLayers = 24;
+constexpr int kGdnLayers = 18;
+constexpr int kAttnLayers = 6;
+constexpr int kHidden = 1024;
+constexpr int kFF = 3584;
+constexpr int kGdnHeads = 16;
+constexpr int kDk = 128;
+constexpr int kDv = 128;
+constexpr int kConvCh = 6144;
+constexpr int kValueDim = 2048;
+constexpr int kGdnProjN = 8224;     // [qkv 6144 | z 2048 | b 16 | a 16]
+constexpr int kQHeads = 8;
+constexpr int kKvHeads = 2;
+constexpr int kHeadDim = 256;
+constexpr int kAttnProjN = 5120;    // [q|gate 4096 | k 512 | v 512]
+constexpr int kRotHalf = 32;
+constexpr int kKvPage = 64;
+constexpr int kPageElems = kKvHeads * kKvPage * kHeadDim;   // bf16 elements per K (or V) page
+constexpr float kEps = 1e-6f;
+
+__host__ __device__ constexpr bool is_attn_layer(int l) { return l % 4 == 3; }
+
+// ---- bf16 <-> f32 (round to nearest even; inputs are finite in this model) -------------------
+__device__ __forceinline__ float bf2f(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+__device__ __forceinline__ uint16_t f2bf(float f) {
+    return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+__device__ __forceinline__ float bfround(float f) { return bf2f(f2bf(f)); }
+__device__ __forceinline__ float lo_bf(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float hi_bf(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+    return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16);
+}
+
+// 1/sqrt(x) with IEEE sqrt and divide (the CPU reference's rsqrt is correctly rounded to ~1 ulp).
+__device__ __forceinline__ float rsqrt_acc(float x) { return __fdiv_rn(1.0f, __fsqrt_rn(x)); }
+__device__ __forceinline__ float sigmoid_acc(float x) { return __fdiv_rn(1.0f, 1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_acc(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// (value, index) with the greedy order: larger value wins, equal values -> lower index wins.
+struct ArgMax {
+    float v;
+    int i;
+};
+__device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
+    return av > bv || (av == bv && ai < bi);
+}
+
+// ---- launcher declarations (defined one per .cu file) -----------------------------------------
+enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2 };
+
+// out[rows][N] (or act / partial argmax) = x[rows][K] . W[N][K]^T, picks the few-row or tiled form.
+// EPI_SWIGLU: W rows interleaved (2f gate, 2f+1 up), out [rows][N/2].
+// EPI_ARGMAX: partials [rows][n_parts] ArgMax, logits (optional) f32 [rows][N]; returns n_parts.
+cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K,
+                          int epi, ArgMax* partials, float* logits, int* n_parts, cudaStream_t st);
+int linear_argmax_parts(int rows, int N);
+cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, int* tokens,
+                                float* top_logit, cudaStream_t st);
+cudaError_t launch_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* out,
+                                cudaStream_t st);
+
+// rows: sum = bf16(x + delta), normed = RMSNorm_zc(sum; w).  If ids != null, x row r is
+// table[ids[r]] (embedding gather).  delta may be null.  row_map (optional) redirects reads:
+// source row = row_map_stride * r + row_map_offset is expressed by the caller through pointers.
+cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* table, int vocab,
+                            const uint16_t* delta, const uint16_t* w, uint16_t* sum_out,
+                            uint16_t* normed_out, int rows, cudaStream_t st);
+
+struct GdnParams {
+    const uint16_t* proj;      // [lanes*T][8224]
+    const uint16_t* conv_w;    // [6144][4]
+    const uint16_t* A_log;     // [16]
+    const uint16_t* dt_bias;   // [16]
+    const uint16_t* norm_w;    // [128]
+    float* S[2];               // two state buffers [lanes][16][128][128]; S[1] may be null
+    uint16_t* win[2];          // two window buffers [lanes][3][6144]; win[1] may be null
+    const int* sel;            // [lanes] live buffer index per lane, or null (= 0)
+    uint16_t* y;               // [lanes*T][2048]
+    int lanes, T;
+    int checkpoint;            // 1: T == 2, state after token 0 goes to the non-live buffer
+};
+cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st);
+
+struct AttnParams {
+    const uint16_t* proj;      // [lanes*T][5120]
+    const uint16_t* q_norm;    // [256]
+    const uint16_t* k_norm;    // [256]
+    uint16_t* kpool;           // pages [n_pages][2][64][256]
+    uint16_t* vpool;
+    const int* page_table;     // [lanes][pages_per_lane] page ids (for this layer)
+    int pages_per_lane;
+    long long table_lane_stride;  // ints between consecutive lanes in page_table
+    const int* slot;           // [lanes] cache slot of the first new token (= positions cached)
+    const int* rope_pos;       // [lanes] rope position of the first new token
+    const float* inv_freq;     // [32]
+    uint16_t* out;             // [lanes*T][2048]
+    int lanes, T;
+    int max_ctx;               // upper bound of slot + T over lanes (sizes shared memory)
+};
+cudaError_t launch_attn(const AttnParams& p, cudaStream_t st);
+cudaError_t attn_init();       // opt in to large dynamic shared memory; call once per device
+
+// state tuple <-> reference layouts
+cudaError_t launch_window_export(const uint16_t* win, float* out, cudaStream_t st);   // [3][6144]x18 handled by caller loop
+cudaError_t launch_window_import(const float* in, uint16_t* win, cudaStream_t st);
+cudaError_t launch_kv_export(const uint16_t* pool, const int* table, int pages, uint16_t* out,
+                             int cap, int n_pos, cudaStream_t st);   // -> [2][cap][256]
+cudaError_t launch_kv_import(const uint16_t* in, int cap, int n_pos, uint16_t* pool, const int* table,
+                             int pages, cudaStream_t st);
+cudaError_t launch_fill_int(int* p, int v, int n, cudaStream_t st);
+cudaError_t launch_add_int(int* p, int v, int n, cudaStream_t st);
+
+}  // namespace q35

@@ -1,0 +1,153 @@
+"""MTP draft / verify rounds through the C-ABI.
+
+On random-init weights the draft almost never agrees with the target (accept rate ~ 0), so, as in
+the reference's own G8a gate (speccheck/gates/run_mtp.py:121-148), the binding checks are:
+the speculative loop emits exactly the tokens of plain greedy decoding, the state after the
+rounds is bit-identical to a sequential replay, and both the accept and the reject branch leave
+positions, draft-cache length and GDN state where a sequential run has them.  The accept branch
+is exercised by handing the verifier the true next token as the candidate.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import q35_oracle as O
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng(pkg, weights):
+    pkg.build_lib.build()
+    e = pkg.Engine(weights, max_rows=256)
+    yield e
+    e.close()
+
+
+def bf(a):
+    return torch.from_numpy(np.asarray(a)).to(torch.bfloat16)
+
+
+def prompts(golden, lanes):
+    base = torch.from_numpy(golden["mtp"]["prompt"]).int()
+    gen = torch.Generator().manual_seed(17)
+    rows = [base] + [torch.randint(0, 248320, (16,), generator=gen).int() for _ in range(lanes - 1)]
+    return torch.stack(rows).cuda()
+
+
+def test_draft_matches_reference(eng, golden):
+    """One draft call on the reference's own (h, y_next, pos): same proposal id."""
+    g = golden["mtp"]
+    st = eng.allocate_state(1, 64)
+    m = eng.mtp_allocate(st, 64)
+    prop = eng.mtp_draft(m, bf(g["draft_h"]).cuda(), torch.tensor(g["draft_y"], dtype=torch.int32).cuda(),
+                         torch.tensor(g["draft_pos"], dtype=torch.int32).cuda())
+    assert int(prop[0]) == int(g["draft_id"][0])
+    m.close()
+    st.close()
+
+
+def test_rounds_equal_plain_greedy_and_sequential_state(eng, golden):
+    lanes, rounds = 3, 8
+    ids = prompts(golden, lanes)
+    # plain greedy
+    sp = eng.allocate_state(lanes, 64)
+    y0, _ = eng.prefill(sp, ids)
+    plain = [y0.clone()]
+    cur = y0
+    for _ in range(rounds):
+        cur = eng.decode_step(sp, cur)
+        plain.append(cur.clone())
+    plain = torch.stack(plain).cpu()                       # [rounds+1, lanes]
+
+    # speculative loop, everything chained on the device
+    ss = eng.allocate_state(lanes, 64)
+    m = eng.mtp_allocate(ss, 64)
+    t, h = eng.prefill(ss, ids, want_normed=True)
+    emitted = [[int(x)] for x in t.tolist()]
+    accepted = 0
+    for _ in range(rounds):
+        pos = (ss.positions + 1).int()
+        d = eng.mtp_draft(m, h, t, pos)
+        emit, n_emit, h = eng.mtp_verify(ss, m, t, d)
+        em, ne = emit.cpu(), n_emit.cpu()
+        for i in range(lanes):
+            emitted[i].extend(em[i, :int(ne[i])].tolist())
+            accepted += int(ne[i]) - 1
+        t = torch.where(n_emit == 2, emit[:, 1], emit[:, 0]).int().contiguous()
+    for i in range(lanes):
+        n = min(len(emitted[i]), rounds + 1)
+        assert emitted[i][:n] == plain[:n, i].tolist(), f"lane {i}"
+    # lanes that never accepted consumed exactly `rounds` tokens: state equals the plain run bit for bit
+    for i in range(lanes):
+        if len(emitted[i]) == rounds + 1:
+            a, b = ss.export_lane(i, 64), sp.export_lane(i, 64)
+            assert a["prefix_len"] == b["prefix_len"] == 16 + rounds
+            assert torch.equal(a["gdn_state"], b["gdn_state"])
+            assert torch.equal(a["conv_window"], b["conv_window"])
+            assert torch.equal(a["kv_keys"][:, :, :16 + rounds], b["kv_keys"][:, :, :16 + rounds])
+    # reference tokens (speculative 'steps' loop of the reference == its plain greedy)
+    ref = golden["mtp"]["tokens_steps"].tolist()
+    common = 0
+    for x, y in zip(emitted[0], ref):
+        if x != y:
+            break
+        common += 1
+    assert common >= 1
+    m.close(); ss.close(); sp.close()
+
+
+def test_accept_and_reject_branches(eng, golden):
+    lanes = 2
+    ids = prompts(golden, lanes)
+    sp = eng.allocate_state(lanes, 64)
+    y0, _ = eng.prefill(sp, ids)
+    seq = [y0.clone()]
+    for _ in range(4):
+        seq.append(eng.decode_step(sp, seq[-1]).clone())
+    # sp has consumed y0..seq[3]; position 16 + 4
+    ss = eng.allocate_state(lanes, 64)
+    m = eng.mtp_allocate(ss, 64)
+    t, h = eng.prefill(ss, ids, want_normed=True)
+    assert torch.equal(t, y0)
+    # round 1: candidate = the true next token -> accept in every lane
+    d = eng.mtp_draft(m, h, t, (ss.positions + 1).int())
+    emit, n_emit, h = eng.mtp_verify(ss, m, t, seq[1])
+    assert n_emit.tolist() == [2, 2]
+    assert torch.equal(emit[:, 0], seq[1]) and torch.equal(emit[:, 1], seq[2])
+    assert ss.positions.tolist() == [18, 18]
+    # round 2: lane 0 gets a wrong candidate (reject), lane 1 the true one (accept)
+    t = emit[:, 1].contiguous()
+    wrong = ((seq[3] + 1) % 248320).int()
+    cand = torch.stack([wrong[0], seq[3][1]]).int().contiguous()
+    d = eng.mtp_draft(m, h, t, (ss.positions + 1).int())
+    emit, n_emit, h = eng.mtp_verify(ss, m, t, cand)
+    assert n_emit.tolist() == [1, 2]
+    assert int(emit[0, 0]) == int(seq[3][0]) and int(emit[0, 1]) == -1
+    assert int(emit[1, 0]) == int(seq[3][1]) and int(emit[1, 1]) == int(seq[4][1])
+    assert ss.positions.tolist() == [19, 20]
+    # lane 1 consumed y0..seq[3] like the plain run: identical state; lane 0 is one token behind
+    a, b = ss.export_lane(1, 64), sp.export_lane(1, 64)
+    assert torch.equal(a["gdn_state"], b["gdn_state"]) and torch.equal(a["conv_window"], b["conv_window"])
+    # lane 0: feed seq[3] through a plain step and it must land on the plain run's state too
+    nxt = eng.decode_step(ss, torch.stack([seq[3][0], seq[4][1]]).int().contiguous())
+    a0, b0 = ss.export_lane(0, 64), sp.export_lane(0, 64)
+    assert a0["prefix_len"] == b0["prefix_len"] == 20
+    assert torch.equal(a0["gdn_state"], b0["gdn_state"]) and torch.equal(a0["conv_window"], b0["conv_window"])
+    assert int(nxt[0]) == int(seq[4][0])
+    m.close(); ss.close(); sp.close()
+
+
+def test_verify_needs_mtp_state(eng, pkg, golden):
+    st = eng.allocate_state(1, 32)
+    other = eng.allocate_state(1, 32)
+    m = eng.mtp_allocate(other, 32)
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(pkg.Q35Error) as ei:
+        eng.mtp_verify(st, m, z, z)
+    assert ei.value.code == 4
+    m.close(); st.close(); other.close()
