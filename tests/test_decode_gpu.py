@@ -106,7 +106,7 @@ def test_decode_teacher_forced_from_imported_state(eng, weights, golden, prefill
     note("teacher_forced_logits_rel_l2", [max(errs_l), float(np.mean(errs_l))])
     note("teacher_forced_token_agreement", [agree, 32, strong_ok, strong, b_agree])
     assert max(errs_n) <= CASCADE and max(errs_l) <= CASCADE
-    assert errs_n[0] <= 2e-2                       # first step: one pass of 24 layers
+    assert errs_n[0] <= 4e-2                       # first step: one pass through 24 layers
     assert strong_ok == strong                     # wide-margin steps must agree
     assert agree >= 24 and b_agree >= 24
     assert int(st.positions[0]) == 96 and int(st.positions[1]) == 96
