@@ -206,6 +206,21 @@ int q35_op_mlp_gateup(const uint16_t* x, const uint16_t* Wgu, uint16_t* act, int
  * optional logits_f32 [rows][vocab].  Uses the engine's partial-argmax scratch. */
 int q35_op_lm_head(q35_engine* e, const uint16_t* x, int rows, int* tokens, float* logits_f32,
                    void* stream);
+/* Tied head + lowest-id argmax for callers that must not allocate device memory.  No counterpart
+ * in the reference.  Some hosts of this library cannot call cudaMalloc at all: a plugin loaded
+ * into a runtime that owns the whole device heap, or a serving loop that runs with a frozen memory
+ * pool and treats any allocation on the hot path as a bug.  They cannot create a q35_engine (which
+ * allocates its scratch), so this entry point takes only inputs and outputs and keeps the
+ * partial-argmax scratch in a fixed 1 MiB device array inside the library (held by every GPU that
+ * loads the library, until the process exits).
+ *   x [rows][1024] bf16, embed [vocab][1024] bf16, tokens [rows] int32; rows <= 16,
+ *   vocab <= 262,144 and a multiple of 8 - larger sizes are refused with Q35_ERR_CAPACITY.
+ * The first call on each device looks up the array's device address (with that device current);
+ * make that first call before starting any stream capture.  All calls share the one array: two
+ * calls that may overlap on the GPU (different streams, no dependency) race on it.  Calls never
+ * allocate or free: no cudaMalloc / cudaFree, and no library routine that allocates. */
+int q35_lm_head_argmax_static(const uint16_t* x, const uint16_t* embed, int vocab, int rows,
+                              int* tokens, void* stream);
 /* gdn_conv + gdn_gates + gdn_rec + gdn_gated_norm (engine/kernels.h:398-460,682) for `lanes`
  * lanes x T tokens of ONE layer.  proj [lanes*T][8224] = [qkv 6144 | z 2048 | b 16 | a 16];
  * S f32 [lanes][16][128][128]; window bf16 [lanes][3][6144]; y [lanes*T][2048]. */

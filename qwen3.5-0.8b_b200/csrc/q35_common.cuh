@@ -79,6 +79,11 @@ cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, i
                                 float* top_logit, cudaStream_t st);
 cudaError_t launch_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* out,
                                 cudaStream_t st);
+// head + argmax for up to kStaticHeadMaxRows rows whose scratch is a fixed device array
+constexpr int kStaticHeadMaxRows = 16;
+constexpr int kStaticHeadMaxVocab = 262144;
+cudaError_t launch_lm_head_static(const uint16_t* x, const uint16_t* embed, int vocab, int rows,
+                                  int* tokens, cudaStream_t st);
 
 // rows: sum = bf16(x + delta), normed = RMSNorm_zc(sum; w).  If ids != null, x row r is
 // table[ids[r]] (embedding gather).  delta may be null.  row_map (optional) redirects reads:

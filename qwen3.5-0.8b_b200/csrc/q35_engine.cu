@@ -797,6 +797,18 @@ extern "C" int q35_op_lm_head(q35_engine* e, const uint16_t* x, int rows, int* t
     return run_head(e, x, rows, tokens, logits_f32, static_cast<cudaStream_t>(stream));
 }
 
+extern "C" int q35_lm_head_argmax_static(const uint16_t* x, const uint16_t* embed, int vocab, int rows,
+                                         int* tokens, void* stream) {
+    REQUIRE(x && embed && tokens, Q35_ERR_ARG, "q35_lm_head_argmax_static: null argument");
+    REQUIRE(aligned16(x) && aligned16(embed), Q35_ERR_ARG, "q35_lm_head_argmax_static: x / embed must be 16-byte aligned");
+    REQUIRE(rows >= 1 && rows <= kStaticHeadMaxRows, Q35_ERR_CAPACITY,
+            "q35_lm_head_argmax_static: rows = %d, the fixed scratch holds at most %d", rows, kStaticHeadMaxRows);
+    REQUIRE(vocab >= 8 && vocab % 8 == 0 && vocab <= kStaticHeadMaxVocab, Q35_ERR_CAPACITY,
+            "q35_lm_head_argmax_static: vocab = %d, must be a multiple of 8 and at most %d", vocab, kStaticHeadMaxVocab);
+    CK(launch_lm_head_static(x, embed, vocab, rows, tokens, static_cast<cudaStream_t>(stream)));
+    return Q35_OK;
+}
+
 extern "C" int q35_op_gdn_step(const uint16_t* proj, const uint16_t* conv_w, const uint16_t* A_log,
                                const uint16_t* dt_bias, const uint16_t* norm_w, float* S, uint16_t* window,
                                uint16_t* y, int lanes, int T, void* stream) {

@@ -468,6 +468,41 @@ cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, i
     return cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------
+// tied head + argmax with the partial-argmax scratch in a fixed device array (no allocation)
+// ------------------------------------------------------------------------------------------------
+// The two-stage argmax needs rows x ceil(vocab / 32) (value, index) partials between its kernels.
+// Here they live in this file-scope array, so the call never allocates.  The array is part of the
+// library image: every GPU that loads the library holds these 1 MiB until the process exits.
+static __device__ __align__(256) ArgMax g_static_partials[kStaticHeadMaxRows * (kStaticHeadMaxVocab / 32)];
+
+cudaError_t launch_lm_head_static(const uint16_t* x, const uint16_t* embed, int vocab, int rows,
+                                  int* tokens, cudaStream_t st) {
+    if (rows < 1 || rows > kStaticHeadMaxRows || vocab < 8 || vocab > kStaticHeadMaxVocab || (vocab & 7))
+        return cudaErrorInvalidValue;
+    // In host code `g_static_partials` is only a handle for the symbol, not a device address, so
+    // the address each device gave the array is looked up once per device and remembered.
+    static ArgMax* dev_ptr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (dev_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_partials);
+        if (e != cudaSuccess) return e;
+        dev_ptr[dev] = static_cast<ArgMax*>(p);
+    }
+    ArgMax* partials = dev_ptr[dev];
+    const int n_parts = (vocab + 31) / 32;
+    // every partial that the second kernel reads is written by the first one in this same call,
+    // so nothing left over from an earlier call needs clearing
+    e = run_gemv<1024, 4, EPI_ARGMAX>(x, embed, nullptr, rows, vocab, partials, nullptr, n_parts, st);
+    if (e != cudaSuccess) return e;
+    argmax_final_kernel<<<rows, 256, 0, st>>>(partials, n_parts, tokens, nullptr);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* out, cudaStream_t st) {
     const size_t total = (size_t)kFF * 128;
     pack_gate_up_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(

@@ -65,6 +65,7 @@ EXPORTS = [
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
     "q35_mtp_state_reset", "q35_mtp_draft", "q35_mtp_verify", "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
+    "q35_lm_head_argmax_static",
 ]
 
 _lib = None
@@ -117,6 +118,18 @@ def rope_inv_freq() -> torch.Tensor:
     """theta^(-2i/64), i = 0..31, in f32 exactly as the reference builds it (speccheck/specimpl.py:153-154)."""
     i = torch.arange(32, dtype=torch.float32)
     return 1.0 / (1e7 ** (2 * i / 64))
+
+
+def lm_head_argmax_static(x: torch.Tensor, embed: torch.Tensor, tokens: torch.Tensor | None = None):
+    """Greedy token of each row of x [rows<=16, 1024] against the tied table embed [vocab, 1024],
+    for callers that may not allocate device memory: needs no Engine, and the library keeps the
+    scratch of its two-stage argmax in a fixed device array.  `tokens` (int32 [rows], device) is
+    the caller's output buffer; pass it to keep this wrapper allocation-free as well."""
+    lib = load_library()
+    if tokens is None:
+        tokens = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    _check(lib.q35_lm_head_argmax_static(_ptr(x), _ptr(embed), embed.shape[0], x.shape[0], _ptr(tokens), _stream()))
+    return tokens
 
 
 class LaneState:
