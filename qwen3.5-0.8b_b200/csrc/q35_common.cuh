@@ -104,6 +104,7 @@ struct GdnParams {
     uint16_t* y;               // [lanes*T][2048]
     int lanes, T;
     int checkpoint;            // 1: T == 2, state after token 0 goes to the non-live buffer
+    int* status;               // device word raised to 1 if a bounded wait expires (may be null)
 };
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st);
 

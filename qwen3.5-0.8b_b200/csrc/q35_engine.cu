@@ -814,7 +814,8 @@ extern "C" int q35_op_gdn_step(const uint16_t* proj, const uint16_t* conv_w, con
                                uint16_t* y, int lanes, int T, void* stream) {
     REQUIRE(proj && conv_w && A_log && dt_bias && norm_w && S && window && y, Q35_ERR_ARG, "q35_op_gdn_step: null argument");
     REQUIRE(lanes >= 1 && lanes <= 65535 && T >= 1, Q35_ERR_ARG, "q35_op_gdn_step: lanes %d T %d", lanes, T);
-    REQUIRE(aligned16(S) && aligned16(conv_w), Q35_ERR_ARG, "q35_op_gdn_step: S / conv_w must be 16-byte aligned");
+    REQUIRE(aligned16(S) && aligned16(conv_w) && aligned16(proj) && aligned16(window), Q35_ERR_ARG,
+            "q35_op_gdn_step: S / conv_w / proj / window must be 16-byte aligned");
     GdnParams gp{};
     gp.proj = proj; gp.conv_w = conv_w; gp.A_log = A_log; gp.dt_bias = dt_bias; gp.norm_w = norm_w;
     gp.S[0] = S; gp.S[1] = nullptr; gp.win[0] = window; gp.win[1] = nullptr; gp.sel = nullptr;
