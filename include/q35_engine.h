@@ -123,6 +123,11 @@ int q35_abi_version(void);
 int q35_engine_create(const q35_config* cfg, const q35_weights* w, void* stream, q35_engine** out);
 int q35_engine_destroy(q35_engine* e);
 int q35_step_census(const q35_engine* e, q35_census* out);
+/* Synchronises the device and reads the engine's status word: 0 = healthy; non-zero = a kernel gave
+ * up a bounded wait (1 GDN tile fetch, 2-4 projection pipeline) and skipped its stores.  The
+ * reference has no device-side waits; its nearest relative is the post-step
+ * RequestState::check_invariants (engine/state.h:99). */
+int q35_engine_status(q35_engine* e, int* status_host);
 /* Per-family kernel timing with CUDA events on the launching stream (replaces the reference's
  * stage_clock, engine/stage_clock.h:59-67).  Between begin and end every kernel of every body is
  * bracketed by an event pair; end synchronises on the last event and returns the summed

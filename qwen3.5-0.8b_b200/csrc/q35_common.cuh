@@ -73,7 +73,19 @@ enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2 };
 // EPI_SWIGLU: W rows interleaved (2f gate, 2f+1 up), out [rows][N/2].
 // EPI_ARGMAX: partials [rows][n_parts] ArgMax, logits (optional) f32 [rows][N]; returns n_parts.
 cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K,
-                          int epi, ArgMax* partials, float* logits, int* n_parts, cudaStream_t st);
+                          int epi, ArgMax* partials, float* logits, int* n_parts, cudaStream_t st,
+                          int* status = nullptr);
+// tcgen05 / TMEM form (q35_gemm_tc.cu), taken by launch_linear for bodies of >= 64 rows
+bool linear_tc_eligible(int rows, int N, int K);
+// split-K route for narrow outputs at few rows: `splits` f32 partials [split][rows][N] in ws, which
+// launch_add_norm sums (delta_parts).  linear_tc_splits returns 1 when the route does not apply.
+constexpr int kMaxSplits = 16;
+constexpr int kSplitMaxRows = 512;
+int linear_tc_splits(int rows, int N, int K, int max_rows_ws);
+cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* ws, int rows, int N, int K,
+                                   int splits, int* status, cudaStream_t st);
+cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
+                             ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st);
 int linear_argmax_parts(int rows, int N);
 cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, int* tokens,
                                 float* top_logit, cudaStream_t st);
@@ -88,9 +100,12 @@ cudaError_t launch_lm_head_static(const uint16_t* x, const uint16_t* embed, int 
 // rows: sum = bf16(x + delta), normed = RMSNorm_zc(sum; w).  If ids != null, x row r is
 // table[ids[r]] (embedding gather).  delta may be null.  row_map (optional) redirects reads:
 // source row = row_map_stride * r + row_map_offset is expressed by the caller through pointers.
+// delta_parts (optional, instead of delta): n_split f32 partials [n_split][rows][1024] whose sum,
+// rounded once to bf16, is the delta.
 cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* table, int vocab,
                             const uint16_t* delta, const uint16_t* w, uint16_t* sum_out,
-                            uint16_t* normed_out, int rows, cudaStream_t st);
+                            uint16_t* normed_out, int rows, cudaStream_t st,
+                            const float* delta_parts = nullptr, int n_split = 0);
 
 struct GdnParams {
     const uint16_t* proj;      // [lanes*T][8224]

@@ -72,6 +72,8 @@ struct q35_engine {
     int parts_cap = 0;
     int *tok2 = nullptr, *tgt = nullptr;     // [max_rows] token scratch
     float* inv_freq = nullptr;
+    int* dev_status = nullptr;               // raised by a kernel whose bounded wait expired
+    float* split_ws = nullptr;               // [kMaxSplits][kSplitMaxRows][1024] f32 K-split partials
     long long weight_bytes = 0;
     std::vector<void*> allocs;
     // optional per-family kernel timing (CUDA events on the launching stream)
@@ -330,6 +332,9 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     CK(dev_alloc(e->allocs, &e->tok2, R));
     CK(dev_alloc(e->allocs, &e->tgt, R));
     CK(dev_alloc(e->allocs, &e->inv_freq, (size_t)32));
+    CK(dev_alloc(e->allocs, &e->split_ws, (size_t)kMaxSplits * kSplitMaxRows * kHidden));
+    CK(dev_alloc(e->allocs, &e->dev_status, (size_t)4));
+    CK(cudaMemsetAsync(e->dev_status, 0, 4 * sizeof(int), st));
     CK(cudaMemcpyAsync(e->inv_freq, e->cfg.rope_inv_freq, 32 * sizeof(float), cudaMemcpyHostToDevice, st));
     CK(cudaStreamSynchronize(st));   // the host-side config copy above must not outlive `cfg`
     return Q35_OK;
@@ -357,6 +362,12 @@ extern "C" int q35_engine_destroy(q35_engine* e) {
     for (cudaEvent_t ev : e->prof_events) cudaEventDestroy(ev);
     free_all(e->allocs);
     delete e;
+    return Q35_OK;
+}
+
+extern "C" int q35_engine_status(q35_engine* e, int* status_host) {
+    REQUIRE(e && status_host, Q35_ERR_ARG, "q35_engine_status: null argument");
+    CK(cudaMemcpy(status_host, e->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
     return Q35_OK;
 }
 
@@ -549,7 +560,7 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
     int gslot = 0, aslot = 0;
     for (int l = 0; l < kLayers; ++l) {
         const PackedLayer& L = e->layers[l];
-        LAUNCH(Q35_FAM_IN_PROJ, launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+        LAUNCH(Q35_FAM_IN_PROJ, launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
         if (L.attn) {
             AttnParams ap{};
             ap.proj = e->proj; ap.q_norm = L.q_norm; ap.k_norm = L.k_norm;
@@ -572,15 +583,32 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
                 gp.win[b] = s->win[b] ? s->win[b] + wo : nullptr;
             }
             gp.sel = s->sel; gp.y = e->mix; gp.lanes = s->lanes; gp.T = T; gp.checkpoint = checkpoint;
+            gp.status = e->dev_status;
             LAUNCH(Q35_FAM_GDN, launch_gdn_step(gp, st));
             ++gslot;
         }
-        LAUNCH(Q35_FAM_OUT_PROJ, launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st));
-        LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
-        LAUNCH(Q35_FAM_MLP_GATEUP, launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st));
-        LAUNCH(Q35_FAM_MLP_DOWN, launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+        {
+            const int sp = linear_tc_splits(rows, kHidden, 2048, kSplitMaxRows);
+            if (sp > 1) {
+                LAUNCH(Q35_FAM_OUT_PROJ, launch_linear_tc_split(e->mix, L.out_w, e->split_ws, rows, kHidden, 2048, sp, e->dev_status, st));
+                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, L.post_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
+            } else {
+                LAUNCH(Q35_FAM_OUT_PROJ, launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
+            }
+        }
+        LAUNCH(Q35_FAM_MLP_GATEUP, launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st, e->dev_status));
         const uint16_t* next_norm = (l + 1 < kLayers) ? e->layers[l + 1].input_norm : e->final_norm;
-        LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, next_norm, e->resid, e->normed, rows, st));
+        {
+            const int sp = linear_tc_splits(rows, kHidden, kFF, kSplitMaxRows);
+            if (sp > 1) {
+                LAUNCH(Q35_FAM_MLP_DOWN, launch_linear_tc_split(e->act, L.down_w, e->split_ws, rows, kHidden, kFF, sp, e->dev_status, st));
+                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, next_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
+            } else {
+                LAUNCH(Q35_FAM_MLP_DOWN, launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, next_norm, e->resid, e->normed, rows, st));
+            }
+        }
     }
     return Q35_OK;
 }
@@ -590,7 +618,7 @@ static int run_head(q35_engine* e, const uint16_t* x, int rows, int* tokens, flo
     REQUIRE(rows <= e->max_rows, Q35_ERR_CAPACITY, "head over %d rows exceeds engine max_rows %d", rows, e->max_rows);
     int n_parts = linear_argmax_parts(rows, e->vocab);
     REQUIRE(n_parts <= e->parts_cap, Q35_ERR_CAPACITY, "argmax partials overflow");
-    LAUNCH(Q35_FAM_HEAD, launch_linear(x, e->embed, nullptr, rows, e->vocab, kHidden, EPI_ARGMAX, e->partials, logits, &n_parts, st));
+    LAUNCH(Q35_FAM_HEAD, launch_linear(x, e->embed, nullptr, rows, e->vocab, kHidden, EPI_ARGMAX, e->partials, logits, &n_parts, st, e->dev_status));
     LAUNCH(Q35_FAM_HEAD, launch_argmax_final(e->partials, n_parts, rows, tokens, nullptr, st));
     return Q35_OK;
 }
@@ -717,9 +745,9 @@ extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_
                          kHidden * sizeof(uint16_t), rows, cudaMemcpyDeviceToDevice, st));
     CK(cudaMemcpy2DAsync(e->pair + kHidden, 2048 * sizeof(uint16_t), e->delta, kHidden * sizeof(uint16_t),
                          kHidden * sizeof(uint16_t), rows, cudaMemcpyDeviceToDevice, st));
-    CK(launch_linear(e->pair, e->mtp_fc, e->resid, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+    CK(launch_linear(e->pair, e->mtp_fc, e->resid, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, L.input_norm, nullptr, e->normed, rows, st));
-    CK(launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+    CK(launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     AttnParams ap{};
     ap.proj = e->proj; ap.q_norm = L.q_norm; ap.k_norm = L.k_norm;
     ap.kpool = m->kpool; ap.vpool = m->vpool; ap.page_table = m->table;
@@ -727,10 +755,10 @@ extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_
     ap.slot = m->n; ap.rope_pos = pos; ap.inv_freq = e->inv_freq;
     ap.out = e->mix; ap.lanes = rows; ap.T = 1; ap.max_ctx = m->max_ctx;
     CK(launch_attn(ap, st));
-    CK(launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+    CK(launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
-    CK(launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st));
-    CK(launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st));
+    CK(launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st, e->dev_status));
+    CK(launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, e->mtp_norm_out, e->resid, e->normed, rows, st));
     int rc = run_head(e, e->normed, rows, proposal, nullptr, st);
     if (rc != Q35_OK) return rc;

@@ -446,7 +446,8 @@ static cudaError_t dispatch(const uint16_t* x, const uint16_t* W, void* out, int
 }
 
 cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K,
-                          int epi, ArgMax* partials, float* logits, int* n_parts_out, cudaStream_t st) {
+                          int epi, ArgMax* partials, float* logits, int* n_parts_out, cudaStream_t st,
+                          int* status) {
     if (rows <= 0 || N <= 0 || (N & 7) || (K != 1024 && K != 2048 && K != 3584))
         return cudaErrorInvalidValue;
     int n_parts = 0;
@@ -454,6 +455,8 @@ cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int r
         n_parts = linear_argmax_parts(rows, N);
         if (n_parts_out) *n_parts_out = n_parts;
     }
+    if (linear_tc_eligible(rows, N, K))
+        return launch_linear_tc(x, W, out, rows, N, K, epi, partials, logits, n_parts, status, st);
     switch (epi) {
         case EPI_PLAIN: return dispatch<EPI_PLAIN>(x, W, out, rows, N, K, partials, logits, n_parts, st);
         case EPI_SWIGLU: return dispatch<EPI_SWIGLU>(x, W, out, rows, N, K, partials, logits, n_parts, st);

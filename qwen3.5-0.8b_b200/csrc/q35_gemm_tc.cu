@@ -1,0 +1,362 @@
+// tcgen05 / TMEM form of the batched projections for bodies of many rows:
+//   out[rows][N] = x[rows][K] . W[N][K]^T   (bf16 operands, f32 accumulate in tensor memory)
+//
+// One CTA computes a 128-row x BN-column output tile.  Operands arrive by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle) into a shared-memory ring (3 stages when two CTAs share
+// an SM, 6-8 when the grid is small and latency-bound); one elected thread
+// issues tcgen05.mma (M = 128, N = BN, K = 16 per instruction) with the accumulator in tensor
+// memory; four epilogue warps read the accumulator back with tcgen05.ld (thread = output row) and
+// apply the plain / SwiGLU / argmax epilogue from registers.  Warp roles: 0 = TMA producer,
+// 1 = TMEM owner + MMA issuer, 2..5 = epilogue.  With the 3-stage ring two CTAs fit per SM, so one
+// tile's epilogue overlaps the other's main loop.  Narrow outputs (N = 1024) at few rows are split
+// along K over gridDim.z; each split stores an f32 partial tile and the consumer (the residual
+// add + norm kernel) sums the partials in a fixed order.  No cluster multicast is used anywhere.
+//
+// Every mbarrier wait is bounded (about one second); on expiry the kernel raises the status word,
+// skips its stores, still frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "q35_common.cuh"
+
+namespace q35 {
+
+namespace {
+
+constexpr int BM = 128, BK = 64;
+constexpr int EPI_PARTIAL = 3;                       // f32 partial tile of one K split
+constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
+constexpr int NUM_THREADS = 192;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (int it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            " selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it == 0) t0 = global_ns();
+        else if (global_ns() - t0 > 1000000000ull) return false;
+    }
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile written by TMA with 128-byte swizzle:
+// rows are 128 bytes, groups of 8 rows are 1024 bytes apart (stride byte offset), descriptor
+// version 1, layout type 2 (128-byte swizzle).  Advancing by 16 k-elements adds 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                  // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset
+    d |= (uint64_t)1 << 46;                  // descriptor version
+    d |= (uint64_t)2 << 61;                  // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+__device__ __forceinline__ uint16_t swiglu_bf16(float gate_acc, float up_acc) {
+    const float g = bfround(gate_acc);
+    const float u = bfround(up_acc);
+    const float s = bfround(silu_acc(g));
+    return f2bf(s * u);
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+               void* __restrict__ out, int M, int N, int num_kb_total, ArgMax* __restrict__ partials,
+               float* __restrict__ logits, int n_parts, int* __restrict__ status) {
+    constexpr int B_BYTES = BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = instr_desc(BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 1];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    if (status != nullptr && *status != 0) return;      // an earlier kernel gave up: do nothing
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    // K split: this CTA covers k-blocks [kb0, kb0 + num_kb)
+    const int kb_per = (num_kb_total + gridDim.z - 1) / gridDim.z;
+    const int kb0 = blockIdx.z * kb_per;
+    const int num_kb = (num_kb_total - kb0) < kb_per ? (num_kb_total - kb0) : kb_per;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;      // 1024-byte aligned ring
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum = smem_u32(&bars[2 * STAGES]);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accum, 1);
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { abort_s = 1; if (status) atomicExch(status, 2); break; }
+                const uint32_t a = tiles + s * STAGE_BYTES;
+                mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                tma_load_2d(a, &tma_x, (kb0 + kb) * BK, m0, full0 + 8 * s);
+                tma_load_2d(a + A_BYTES, &tma_w, (kb0 + kb) * BK, n0, full0 + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(full0 + 8 * s, ph)) { abort_s = 1; if (status) atomicExch(status, 3); ok = false; break; }
+                tc_fence_after();
+                const uint32_t a = tiles + s * STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)
+                    tc_mma(tmem_base, smem_desc_sw128(a + k * 32), smem_desc_sw128(a + A_BYTES + k * 32), IDESC,
+                           (kb | k) != 0 ? 1u : 0u);
+                tc_commit(empty0 + 8 * s);       // frees the stage once these MMAs have read it
+            }
+            if (ok) tc_commit(accum);            // accumulator complete
+        }
+    } else {
+        // ---- epilogue: thread = output row (TMEM lane), registers = columns ----------------------
+        const bool ready = mbar_wait(accum, 0);
+        if (!ready && lane == 0 && status) atomicExch(status, 4);
+        tc_fence_after();
+        const int q = warp & 3;                                  // TMEM lane quarter this warp may read
+        const int row = m0 + q * 32 + lane;
+        float bv = -INFINITY;
+        int bi = 0x7fffffff;
+        if (ready) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, r);
+                const int col0 = n0 + c * 32;
+                if (row >= M || col0 >= N) continue;
+                const int valid = (N - col0) < 32 ? (N - col0) : 32;
+                if (EPI == EPI_PARTIAL) {
+                    float* o = static_cast<float*>(out) + ((size_t)blockIdx.z * M + row) * N + col0;
+                    if (valid == 32) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            reinterpret_cast<uint4*>(o)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) o[j] = __uint_as_float(r[j]);
+                    }
+                } else if (EPI == EPI_PLAIN) {
+                    uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * N + col0;
+                    if (valid == 32) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 w;
+                            w.x = pack_bf2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            w.y = pack_bf2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            w.z = pack_bf2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            w.w = pack_bf2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            reinterpret_cast<uint4*>(o)[v] = w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) o[j] = f2bf(__uint_as_float(r[j]));
+                    }
+                } else if (EPI == EPI_SWIGLU) {
+                    uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * (N >> 1) + (col0 >> 1);
+                    if (valid == 32) {
+#pragma unroll
+                        for (int v = 0; v < 2; ++v) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int b = 16 * v + 4 * j;
+                                w[j] = (uint32_t)swiglu_bf16(__uint_as_float(r[b]), __uint_as_float(r[b + 1])) |
+                                       ((uint32_t)swiglu_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3])) << 16);
+                            }
+                            reinterpret_cast<uint4*>(o)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (2 * j + 1 < valid)
+                                o[j] = swiglu_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float v = __uint_as_float(r[j]);
+                        if (j < valid && v > bv) { bv = v; bi = col0 + j; }      // ascending scan: lowest id on ties
+                    }
+                    if (logits != nullptr) {
+                        float* lg = logits + (size_t)row * N + col0;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < valid) lg[j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            if (EPI == EPI_ARGMAX && row < M) partials[(size_t)row * n_parts + blockIdx.y] = ArgMax{bv, bi};
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ---- host side: tensor maps -------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// bf16 matrix [rows][K] row-major, box = 64 k-elements x box_rows rows, 128-byte swizzle, zero fill
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, int EPI>
+cudaError_t run_tc(const uint16_t* x, const uint16_t* W, void* out, int M, int N, int K, int splits,
+                   ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + BN * BK * 2) + 1024;
+    static bool attr_done = false;
+    auto kern = gemm_tc_kernel<BN, STAGES, EPI>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, W, N, K, BN)) return cudaErrorInvalidValue;
+    dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, splits);
+    kern<<<grid, NUM_THREADS, smem, st>>>(mx, mw, out, M, N, K / BK, partials, logits, n_parts, status);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool linear_tc_eligible(int rows, int N, int K) { return rows >= 64 && N >= 128 && K % BK == 0; }
+
+// K splits the tcgen05 form would use for a plain projection (1 = no split).
+int linear_tc_splits(int rows, int N, int K, int max_rows_ws) {
+    if (!linear_tc_eligible(rows, N, K) || N > 1024 || rows > max_rows_ws) return 1;
+    const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
+    if (tiles >= 100) return 1;
+    const int num_kb = K / BK;
+    int splits = (148 + tiles - 1) / tiles;
+    if (splits > num_kb / 4) splits = num_kb / 4;        // at least 4 k-blocks per split
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits < 2) return 1;
+    const int kb_per = (num_kb + splits - 1) / splits;
+    return (num_kb + kb_per - 1) / kb_per;               // every split gets at least one k-block
+}
+
+cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* ws, int rows, int N, int K,
+                                   int splits, int* status, cudaStream_t st) {
+    return run_tc<128, 4, EPI_PARTIAL>(x, W, ws, rows, N, K, splits, nullptr, nullptr, 0, status, st);
+}
+
+cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
+                             ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
+    const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
+    if (epi == EPI_ARGMAX)
+        return run_tc<128, 3, EPI_ARGMAX>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+    if (epi == EPI_PLAIN) {
+        if (tiles < 100) return run_tc<64, 8, EPI_PLAIN>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+        if (tiles <= 148) return run_tc<128, 6, EPI_PLAIN>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+        return run_tc<128, 3, EPI_PLAIN>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+    }
+    if (epi == EPI_SWIGLU) {
+        if (tiles < 100) return run_tc<64, 8, EPI_SWIGLU>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+        if (tiles <= 148) return run_tc<128, 6, EPI_SWIGLU>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+        return run_tc<128, 3, EPI_SWIGLU>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace q35

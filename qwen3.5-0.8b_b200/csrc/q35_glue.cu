@@ -12,7 +12,8 @@ __global__ void __launch_bounds__(256)
 add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
                 const uint16_t* __restrict__ table, int vocab, const uint16_t* __restrict__ delta,
                 const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
-                uint16_t* __restrict__ normed_out, int rows) {
+                uint16_t* __restrict__ normed_out, int rows, const float* __restrict__ delta_parts,
+                int n_split) {
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -32,15 +33,28 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
         const uint4 a = *reinterpret_cast<const uint4*>(src + off);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
         uint32_t dw[4] = {0, 0, 0, 0};
+        const bool has_delta = delta != nullptr || delta_parts != nullptr;
         if (delta != nullptr) {
             const uint4 d = *reinterpret_cast<const uint4*>(delta + (size_t)row * kHidden + off);
             dw[0] = d.x; dw[1] = d.y; dw[2] = d.z; dw[3] = d.w;
+        } else if (delta_parts != nullptr) {
+            // K-split projection: sum the partial tiles in split order, round once to bf16
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int z = 0; z < n_split; ++z) {
+                const float4* pp = reinterpret_cast<const float4*>(
+                    delta_parts + ((size_t)z * rows + row) * kHidden + off);
+                const float4 p0 = pp[0], p1 = pp[1];
+                acc[0] += p0.x; acc[1] += p0.y; acc[2] += p0.z; acc[3] += p0.w;
+                acc[4] += p1.x; acc[5] += p1.y; acc[6] += p1.z; acc[7] += p1.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dw[j] = pack_bf2(acc[2 * j], acc[2 * j + 1]);
         }
         uint32_t sw[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             float lo = lo_bf(aw[j]), hi = hi_bf(aw[j]);
-            if (delta != nullptr) {
+            if (has_delta) {
                 lo = bfround(lo + lo_bf(dw[j]));
                 hi = bfround(hi + hi_bf(dw[j]));
             }
@@ -75,9 +89,10 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
 
 cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* table, int vocab,
                             const uint16_t* delta, const uint16_t* w, uint16_t* sum_out,
-                            uint16_t* normed_out, int rows, cudaStream_t st) {
+                            uint16_t* normed_out, int rows, cudaStream_t st, const float* delta_parts,
+                            int n_split) {
     add_norm_kernel<<<(rows + 7) / 8, 256, 0, st>>>(x, ids, table, vocab, delta, w, sum_out,
-                                                    normed_out, rows);
+                                                    normed_out, rows, delta_parts, n_split);
     return cudaGetLastError();
 }
 

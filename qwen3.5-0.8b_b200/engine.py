@@ -59,7 +59,7 @@ class Census(C.Structure):
 
 EXPORTS = [
     "q35_last_error", "q35_abi_version", "q35_engine_create", "q35_engine_destroy", "q35_step_census",
-    "q35_profile_begin", "q35_profile_end",
+    "q35_profile_begin", "q35_profile_end", "q35_engine_status",
     "q35_state_sizes_of", "q35_state_create", "q35_state_destroy", "q35_state_reset",
     "q35_state_positions", "q35_state_note_advance", "q35_state_export_lane", "q35_state_import_lane",
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
@@ -272,6 +272,12 @@ class Engine:
         # the library copied everything except the embedding table, which it reads in place
         self.embed = dev[W.LM + "embed_tokens.weight"]
         del dev
+
+    def status(self) -> int:
+        """0 when healthy; non-zero when a kernel's bounded wait expired (synchronises the device)."""
+        v = C.c_int(0)
+        _check(self.lib.q35_engine_status(self.handle, C.byref(v)))
+        return v.value
 
     # ---- census -------------------------------------------------------------------------------
     def census(self) -> dict:

@@ -45,6 +45,7 @@ def eng(pkg, weights):
     pkg.build_lib.build()
     e = pkg.Engine(weights, max_rows=4096)
     yield e
+    assert e.status() == 0, "a kernel gave up a bounded wait"
     e.close()
 
 
