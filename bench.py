@@ -282,7 +282,8 @@ def main():
     pkg = load_package()
     pkg.build_lib.build()
     params = pkg.weights.make_weights(seed=0)
-    rows = max(min(8 * args.lanes, 32768), 2 * args.lanes, 1024)
+    # scratch rows: 64 prompt tokens per lane per prefill body (the chunk-64 GDN scan), capped at 256 Ki rows
+    rows = max(min(64 * args.lanes, 262144), 2 * args.lanes, 1024)
     eng = pkg.Engine(params, max_rows=rows)
     sampler = ClockSampler(local) if rank == 0 else None
     m = measure(pkg, eng, args.lanes, args.prompt, args.steps, args.warmup, dist, sampler)
@@ -295,7 +296,8 @@ def main():
            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 * args.lanes,
                    "d2h_bytes_per_step": 4 * args.lanes, "ms_per_step": round(m["ms_e2e"] / m["steps_e2e"], 5)},
            "gpu_launches": eng.census()["launches_decode"] * m["steps_dev"],
-           "clocks": m["clocks"], "roofline": roofline_of(eng, m), "prefill_s": round(m["prefill_s"], 2)}
+           "clocks": m["clocks"], "roofline": roofline_of(eng, m), "prefill_s": round(m["prefill_s"], 2),
+           "prefill_tok_per_s": round(args.lanes * args.prompt / m["prefill_s"], 1)}
     sweep = []
     if rank == 0 and args.sweep:
         for L in [int(x) for x in args.sweep.split(",") if x]:

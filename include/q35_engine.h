@@ -228,8 +228,11 @@ int q35_lm_head_argmax_static(const uint16_t* x, const uint16_t* embed, int voca
                               int* tokens, void* stream);
 /* gdn_conv + gdn_gates + gdn_rec + gdn_gated_norm (engine/kernels.h:398-460,682) for `lanes`
  * lanes x T tokens of ONE layer.  proj [lanes*T][8224] = [qkv 6144 | z 2048 | b 16 | a 16];
- * S f32 [lanes][16][128][128]; window bf16 [lanes][3][6144]; y [lanes*T][2048]. */
-int q35_op_gdn_step(const uint16_t* proj, const uint16_t* conv_w, const uint16_t* A_log,
+ * S f32 [lanes][16][128][128]; window bf16 [lanes][3][6144]; y [lanes*T][2048].
+ * T < 32: token-by-token recurrence (the decode form).  T >= 32: the chunk-64 scan of the
+ * reference's prefill (speccheck/specimpl.py:187-235), which overwrites the q|k|v columns of proj
+ * with the conv outputs. */
+int q35_op_gdn_step(uint16_t* proj, const uint16_t* conv_w, const uint16_t* A_log,
                     const uint16_t* dt_bias, const uint16_t* norm_w, float* S, uint16_t* window,
                     uint16_t* y, int lanes, int T, void* stream);
 /* attn_decode_layer (engine/kernels.h:730-906) for `lanes` lanes x T new tokens of ONE layer over a

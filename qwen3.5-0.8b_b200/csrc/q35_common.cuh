@@ -122,6 +122,10 @@ struct GdnParams {
     int* status;               // device word raised to 1 if a bounded wait expires (may be null)
 };
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st);
+// chunk-64 form for bodies of many tokens per lane (no checkpoint); overwrites the raw q|k|v
+// columns of p.proj with the conv outputs
+constexpr int kGdnChunkMinT = 32;
+cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st);
 
 struct AttnParams {
     const uint16_t* proj;      // [lanes*T][5120]

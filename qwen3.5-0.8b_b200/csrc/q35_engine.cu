@@ -70,6 +70,7 @@ struct q35_engine {
              *act = nullptr, *pair = nullptr, *last_normed = nullptr;
     ArgMax* partials = nullptr;
     int parts_cap = 0;
+    int head_rows_cap = 0;                   // rows the head's partial-argmax scratch holds
     int *tok2 = nullptr, *tgt = nullptr;     // [max_rows] token scratch
     float* inv_freq = nullptr;
     int* dev_status = nullptr;               // raised by a kernel whose bounded wait expired
@@ -325,10 +326,11 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     CK(dev_alloc(e->allocs, &e->mix, R * 2048));
     CK(dev_alloc(e->allocs, &e->delta, R * kHidden));
     CK(dev_alloc(e->allocs, &e->act, R * kFF));
-    CK(dev_alloc(e->allocs, &e->pair, R * 2048));
+    CK(dev_alloc(e->allocs, &e->pair, (e->has_mtp ? (size_t)e->head_rows_cap : 1) * 2048));
     CK(dev_alloc(e->allocs, &e->last_normed, R * kHidden));
     e->parts_cap = (e->vocab + 31) / 32;
-    CK(dev_alloc(e->allocs, &e->partials, R * (size_t)e->parts_cap));
+    e->head_rows_cap = e->max_rows < 16384 ? e->max_rows : 16384;   // the head sees lanes (or 2 x lanes) rows, never a whole prefill body
+    CK(dev_alloc(e->allocs, &e->partials, (size_t)e->head_rows_cap * e->parts_cap));
     CK(dev_alloc(e->allocs, &e->tok2, R));
     CK(dev_alloc(e->allocs, &e->tgt, R));
     CK(dev_alloc(e->allocs, &e->inv_freq, (size_t)32));
@@ -584,7 +586,10 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
             }
             gp.sel = s->sel; gp.y = e->mix; gp.lanes = s->lanes; gp.T = T; gp.checkpoint = checkpoint;
             gp.status = e->dev_status;
-            LAUNCH(Q35_FAM_GDN, launch_gdn_step(gp, st));
+            if (!checkpoint && T >= kGdnChunkMinT)
+                LAUNCH(Q35_FAM_GDN, launch_gdn_chunked(gp, st));
+            else
+                LAUNCH(Q35_FAM_GDN, launch_gdn_step(gp, st));
             ++gslot;
         }
         {
@@ -615,7 +620,7 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
 
 // tied head + device argmax over `rows` rows of x
 static int run_head(q35_engine* e, const uint16_t* x, int rows, int* tokens, float* logits, cudaStream_t st) {
-    REQUIRE(rows <= e->max_rows, Q35_ERR_CAPACITY, "head over %d rows exceeds engine max_rows %d", rows, e->max_rows);
+    REQUIRE(rows <= e->head_rows_cap, Q35_ERR_CAPACITY, "head over %d rows exceeds the engine's %d head rows", rows, e->head_rows_cap);
     int n_parts = linear_argmax_parts(rows, e->vocab);
     REQUIRE(n_parts <= e->parts_cap, Q35_ERR_CAPACITY, "argmax partials overflow");
     LAUNCH(Q35_FAM_HEAD, launch_linear(x, e->embed, nullptr, rows, e->vocab, kHidden, EPI_ARGMAX, e->partials, logits, &n_parts, st, e->dev_status));
@@ -837,7 +842,7 @@ extern "C" int q35_lm_head_argmax_static(const uint16_t* x, const uint16_t* embe
     return Q35_OK;
 }
 
-extern "C" int q35_op_gdn_step(const uint16_t* proj, const uint16_t* conv_w, const uint16_t* A_log,
+extern "C" int q35_op_gdn_step(uint16_t* proj, const uint16_t* conv_w, const uint16_t* A_log,
                                const uint16_t* dt_bias, const uint16_t* norm_w, float* S, uint16_t* window,
                                uint16_t* y, int lanes, int T, void* stream) {
     REQUIRE(proj && conv_w && A_log && dt_bias && norm_w && S && window && y, Q35_ERR_ARG, "q35_op_gdn_step: null argument");
@@ -848,7 +853,10 @@ extern "C" int q35_op_gdn_step(const uint16_t* proj, const uint16_t* conv_w, con
     gp.proj = proj; gp.conv_w = conv_w; gp.A_log = A_log; gp.dt_bias = dt_bias; gp.norm_w = norm_w;
     gp.S[0] = S; gp.S[1] = nullptr; gp.win[0] = window; gp.win[1] = nullptr; gp.sel = nullptr;
     gp.y = y; gp.lanes = lanes; gp.T = T; gp.checkpoint = 0;
-    CK(launch_gdn_step(gp, static_cast<cudaStream_t>(stream)));
+    if (T >= kGdnChunkMinT)
+        CK(launch_gdn_chunked(gp, static_cast<cudaStream_t>(stream)));
+    else
+        CK(launch_gdn_step(gp, static_cast<cudaStream_t>(stream)));
     return Q35_OK;
 }
 

@@ -1,0 +1,417 @@
+// Chunked (chunk = 64 tokens) GatedDeltaNet prefill: the UT-transform form of the delta rule.
+//
+// For a body that carries T >= 32 tokens per lane the token-by-token recurrence is replaced by
+//   (1) gdn_conv_prep_kernel : causal conv1d + SiLU over all T rows of a lane, in place over the
+//       raw q|k|v columns of the projection buffer, and the conv-window roll;
+//   (2) gdn_chunk_kernel     : one CTA per (head, lane) walks the chunks with the 128x128 f32 state
+//       resident in shared memory.  Per chunk: row scalars (L2 norms, beta, log-decay prefix sum),
+//       G = K K^T and P = Q K^T masked by the pairwise decay, ONE unit-lower-triangular solve for
+//       both right-hand sides [beta v | beta e^cum k], then
+//           v_new = nv - kc S ;  o = (e^cum q) S + intra v_new ;  S = e^cumC S + (e^(cumC-cum) k)^T v_new
+//       and the gated RMSNorm of o, all in f32 like the reference (speccheck/specimpl.py:187-235).
+//       Rows past T are padded with beta = 0, g = 0, q = k = v = 0 (they neither read nor write S).
+// The reference engine ships only the sequential span kernel (engine/gdn_rec_reg16_kernels.h); its
+// chunked prototype is disabled (engine/kernels_gdn.cpp:430-446).
+#include "q35_common.cuh"
+
+namespace q35 {
+
+namespace {
+
+constexpr int C = 64;                  // chunk length
+constexpr int KQ_LD = 136;             // bf16 row stride of the q / k chunk tiles (272 B: conflict-free 16-B reads)
+constexpr int X_LD = 256;              // f32 row stride of [nv | kc]
+constexpr int T_LD = 68;               // f32 row stride of the 64x64 matrices
+constexpr int kOffZ = 6144, kOffB = 8192, kOffA = 8208;
+
+constexpr size_t kChunkSmem = (size_t)128 * 128 * 4 + (size_t)C * X_LD * 4 + 2 * (size_t)C * KQ_LD * 2 +
+                              2 * (size_t)C * T_LD * 4 + 8 * C * 4;
+
+// ---- (1) conv + SiLU over a lane's T rows, in place; window roll -------------------------------
+// grid (lanes, 12), 256 threads, 2 adjacent channels per thread.
+__global__ void __launch_bounds__(256)
+gdn_conv_prep_kernel(uint16_t* __restrict__ proj, const uint16_t* __restrict__ conv_w,
+                     uint16_t* __restrict__ win0, uint16_t* __restrict__ win1, const int* __restrict__ sel,
+                     int T) {
+    const int lane_id = blockIdx.x;
+    const int c = (blockIdx.y * 256 + threadIdx.x) * 2;
+    uint16_t* win = ((sel != nullptr && (sel[lane_id] & 1)) ? win1 : win0) + (size_t)lane_id * 3 * kConvCh;
+    float tap[2][4], w[2][3];
+    {
+        const uint4 tw = *reinterpret_cast<const uint4*>(conv_w + (size_t)c * 4);
+        tap[0][0] = lo_bf(tw.x); tap[0][1] = hi_bf(tw.x); tap[0][2] = lo_bf(tw.y); tap[0][3] = hi_bf(tw.y);
+        tap[1][0] = lo_bf(tw.z); tap[1][1] = hi_bf(tw.z); tap[1][2] = lo_bf(tw.w); tap[1][3] = hi_bf(tw.w);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const uint32_t v = *reinterpret_cast<const uint32_t*>(win + j * kConvCh + c);
+            w[0][j] = lo_bf(v); w[1][j] = hi_bf(v);
+        }
+    }
+    uint16_t* p = proj + (size_t)lane_id * T * kGdnProjN + c;
+#pragma unroll 4
+    for (int t = 0; t < T; ++t, p += kGdnProjN) {
+        const uint32_t rv = *reinterpret_cast<const uint32_t*>(p);
+        const float raw[2] = {lo_bf(rv), hi_bf(rv)};
+        float u[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            float acc = __fmul_rn(w[e][0], tap[e][0]);
+            acc = __fadd_rn(acc, __fmul_rn(w[e][1], tap[e][1]));
+            acc = __fadd_rn(acc, __fmul_rn(w[e][2], tap[e][2]));
+            acc = __fadd_rn(acc, __fmul_rn(raw[e], tap[e][3]));
+            u[e] = bfround(silu_acc(bfround(acc)));
+            w[e][0] = w[e][1]; w[e][1] = w[e][2]; w[e][2] = raw[e];
+        }
+        *reinterpret_cast<uint32_t*>(p) = pack_bf2(u[0], u[1]);
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) *reinterpret_cast<uint32_t*>(win + j * kConvCh + c) = pack_bf2(w[0][j], w[1][j]);
+}
+
+__device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
+    f[0] = lo_bf(v.x); f[1] = hi_bf(v.x); f[2] = lo_bf(v.y); f[3] = hi_bf(v.y);
+    f[4] = lo_bf(v.z); f[5] = hi_bf(v.z); f[6] = lo_bf(v.w); f[7] = hi_bf(v.w);
+}
+
+// ---- (2) the chunk scan ------------------------------------------------------------------------
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__ A_log,
+                 const uint16_t* __restrict__ dt_bias, const uint16_t* __restrict__ norm_w,
+                 float* __restrict__ S0, float* __restrict__ S1, const int* __restrict__ sel,
+                 uint16_t* __restrict__ y, int T) {
+    extern __shared__ __align__(16) unsigned char smem_chunk[];
+    float* S_s = reinterpret_cast<float*>(smem_chunk);                 // [128][128]  S[dk][dv]
+    float* X_s = S_s + 128 * 128;                                      // [64][256]   [nv | kc]
+    uint16_t* K_s = reinterpret_cast<uint16_t*>(X_s + C * X_LD);       // [64][136] bf16
+    uint16_t* Q_s = K_s + C * KQ_LD;                                   // [64][136] bf16
+    float* Tri_s = reinterpret_cast<float*>(Q_s + C * KQ_LD);          // [64][68]   strictly lower part used
+    float* Int_s = Tri_s + C * T_LD;                                   // [64][68]
+    float* sc = Int_s + C * T_LD;                                      // 8 x [64] row scalars
+    float* cum_s = sc;            // inclusive prefix sum of the log decay
+    float* beta_s = sc + 64;
+    float* kinv_s = sc + 128;     // 1 / |k|
+    float* qsc_s = sc + 192;      // 1 / |q| * 128^-1/2 * e^cum
+    float* ecum_s = sc + 256;     // e^cum
+    float* kout_s = sc + 320;     // 1 / |k| * e^(cumC - cum)
+    float* g_s = sc + 384;
+    float* qn_s = sc + 448;       // 1 / |q| * 128^-1/2
+
+    const int h = blockIdx.x, lane_id = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    float* S_g = ((sel != nullptr && (sel[lane_id] & 1)) ? S1 : S0) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
+    const float negA = -expf(bf2f(A_log[h]));
+    const float dtb = bf2f(dt_bias[h]);
+    const float q_scale = 0.08838834764831845f;
+
+    for (int i = tid; i < 128 * 32; i += 256)
+        reinterpret_cast<float4*>(S_s)[i] = reinterpret_cast<const float4*>(S_g)[i];
+
+    const int n_chunks = (T + C - 1) / C;
+    for (int ck = 0; ck < n_chunks; ++ck) {
+        const int t0 = ck * C;
+        const int valid = (T - t0) < C ? (T - t0) : C;
+        const uint16_t* pr0 = proj + ((size_t)lane_id * T + t0) * kGdnProjN;
+
+        // ---- load q, k tiles (bf16, zero rows past T) and the gate inputs -------------------------
+        for (int i = tid; i < C * 16; i += 256) {
+            const int r = i >> 4, cc = i & 15;
+            uint4 kq = make_uint4(0, 0, 0, 0), qq = make_uint4(0, 0, 0, 0);
+            if (r < valid) {
+                const uint16_t* pr = pr0 + (size_t)r * kGdnProjN;
+                qq = *reinterpret_cast<const uint4*>(pr + h * 128 + cc * 8);
+                kq = *reinterpret_cast<const uint4*>(pr + 2048 + h * 128 + cc * 8);
+            }
+            *reinterpret_cast<uint4*>(K_s + r * KQ_LD + cc * 8) = kq;
+            *reinterpret_cast<uint4*>(Q_s + r * KQ_LD + cc * 8) = qq;
+        }
+        if (tid < C) {
+            float beta = 0.f, g = 0.f;
+            if (tid < valid) {
+                const uint16_t* pr = pr0 + (size_t)tid * kGdnProjN;
+                beta = sigmoid_acc(bf2f(pr[kOffB + h]));
+                const float sp_in = bf2f(pr[kOffA + h]) + dtb;
+                const float sp = sp_in > 20.0f ? sp_in : log1pf(expf(sp_in));
+                g = __fmul_rn(negA, sp);
+            }
+            beta_s[tid] = beta;
+            g_s[tid] = g;
+        }
+        __syncthreads();
+
+        // ---- row scalars: L2 norms (warp w takes rows 8w..8w+7), prefix sum of g -----------------
+        float my_qinv[8];
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+            const int r = warp * 8 + rr;
+            const uint2 kv = *reinterpret_cast<const uint2*>(K_s + r * KQ_LD + ln * 4);
+            const uint2 qv = *reinterpret_cast<const uint2*>(Q_s + r * KQ_LD + ln * 4);
+            float ks = lo_bf(kv.x) * lo_bf(kv.x) + hi_bf(kv.x) * hi_bf(kv.x) + lo_bf(kv.y) * lo_bf(kv.y) + hi_bf(kv.y) * hi_bf(kv.y);
+            float qs = lo_bf(qv.x) * lo_bf(qv.x) + hi_bf(qv.x) * hi_bf(qv.x) + lo_bf(qv.y) * lo_bf(qv.y) + hi_bf(qv.y) * hi_bf(qv.y);
+            ks = warp_sum(ks);
+            qs = warp_sum(qs);
+            my_qinv[rr] = rsqrt_acc(qs + 1e-6f);
+            if (ln == 0) kinv_s[r] = rsqrt_acc(ks + 1e-6f);
+        }
+        if (tid == 0) {
+            float c = 0.f;
+            for (int i = 0; i < C; ++i) { c += g_s[i]; cum_s[i] = c; }
+        }
+        __syncthreads();
+        {
+            const float cumC = cum_s[C - 1];
+            if (ln == 0) {
+#pragma unroll
+                for (int rr = 0; rr < 8; ++rr) {
+                    const int r = warp * 8 + rr;
+                    const float e = expf(cum_s[r]);
+                    ecum_s[r] = e;
+                    qn_s[r] = __fmul_rn(my_qinv[rr], q_scale);
+                    qsc_s[r] = __fmul_rn(__fmul_rn(my_qinv[rr], q_scale), e);
+                    kout_s[r] = __fmul_rn(kinv_s[r], expf(cumC - cum_s[r]));
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- right-hand sides into X: [ beta v | beta e^cum k_hat ] --------------------------------
+        for (int i = tid; i < C * 16; i += 256) {
+            const int r = i >> 4, cc = i & 15;
+            float vf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, kf[8];
+            if (r < valid)
+                unpack8f(*reinterpret_cast<const uint4*>(pr0 + (size_t)r * kGdnProjN + 4096 + h * 128 + cc * 8), vf);
+            unpack8f(*reinterpret_cast<const uint4*>(K_s + r * KQ_LD + cc * 8), kf);
+            const float b = beta_s[r];
+            const float kb = __fmul_rn(__fmul_rn(kinv_s[r], b), ecum_s[r]);
+            float* xv = X_s + r * X_LD + cc * 8;
+            float* xk = xv + 128;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { xv[e] = vf[e] * b; xk[e] = kf[e] * kb; }
+        }
+
+        // ---- G = K K^T, P = Q K^T (4x4 interleaved block per thread), masked by the pair decay ----
+        {
+            const int ti = tid >> 4, tj = tid & 15;
+            float accG[4][4], accP[4][4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) { accG[a][b] = 0.f; accP[a][b] = 0.f; }
+            for (int d0 = 0; d0 < 128; d0 += 8) {
+                float kr[4][8], qr[4][8], kc[4][8];
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    unpack8f(*reinterpret_cast<const uint4*>(K_s + (ti + 16 * a) * KQ_LD + d0), kr[a]);
+                    unpack8f(*reinterpret_cast<const uint4*>(Q_s + (ti + 16 * a) * KQ_LD + d0), qr[a]);
+                    unpack8f(*reinterpret_cast<const uint4*>(K_s + (tj + 16 * a) * KQ_LD + d0), kc[a]);
+                }
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            accG[a][b] += kr[a][e] * kc[b][e];
+                            accP[a][b] += qr[a][e] * kc[b][e];
+                        }
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int i = ti + 16 * a;
+                const float ci = cum_s[i];
+                const float gi = __fmul_rn(beta_s[i], kinv_s[i]);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int j = tj + 16 * b;
+                    float tri = 0.f, intra = 0.f;
+                    if (j <= i) {
+                        const float dec = expf(ci - cum_s[j]);
+                        const float kj = kinv_s[j];
+                        if (j < i) tri = accG[a][b] * gi * kj * dec;
+                        intra = accP[a][b] * kj * dec;      // times the q row scale below
+                    }
+                    Tri_s[i * T_LD + j] = tri;
+                    Int_s[i * T_LD + j] = intra;
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- solve (I + L) X = B by forward substitution, one column of X per thread ---------------
+        {
+            float x[C];
+#pragma unroll
+            for (int i = 0; i < C; ++i) {
+                float acc = X_s[i * X_LD + tid];
+#pragma unroll
+                for (int j = 0; j < i; ++j) acc -= Tri_s[i * T_LD + j] * x[j];
+                x[i] = acc;
+            }
+#pragma unroll
+            for (int i = 0; i < C; ++i) X_s[i * X_LD + tid] = x[i];
+        }
+        __syncthreads();
+
+        // ---- v_new = nv - kc S   (thread: 8 rows x 4 columns; a warp shares its 8 rows) ------------
+        const int r8 = warp * 8, c4 = ln * 4;
+        {
+            float acc[8][4];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+            for (int d0 = 0; d0 < 128; d0 += 4) {
+                float4 sv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sv[e] = *reinterpret_cast<const float4*>(S_s + (d0 + e) * 128 + c4);
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    const float4 kc4 = *reinterpret_cast<const float4*>(X_s + (r8 + a) * X_LD + 128 + d0);
+                    const float kcv[4] = {kc4.x, kc4.y, kc4.z, kc4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc[a][0] += kcv[e] * sv[e].x; acc[a][1] += kcv[e] * sv[e].y;
+                        acc[a][2] += kcv[e] * sv[e].z; acc[a][3] += kcv[e] * sv[e].w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                float4* p = reinterpret_cast<float4*>(X_s + (r8 + a) * X_LD + c4);
+                float4 nv = *p;
+                nv.x -= acc[a][0]; nv.y -= acc[a][1]; nv.z -= acc[a][2]; nv.w -= acc[a][3];
+                *p = nv;
+            }
+        }
+        __syncthreads();
+
+        // ---- o = (q row-scaled) S + intra v_new ; gated RMSNorm ; store y -------------------------
+        {
+            float acc[8][4], acc2[8][4];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) { acc[a][b] = 0.f; acc2[a][b] = 0.f; }
+            for (int d0 = 0; d0 < 128; d0 += 8) {
+                float4 sv[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] = *reinterpret_cast<const float4*>(S_s + (d0 + e) * 128 + c4);
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    float qf[8];
+                    unpack8f(*reinterpret_cast<const uint4*>(Q_s + (r8 + a) * KQ_LD + d0), qf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        acc[a][0] += qf[e] * sv[e].x; acc[a][1] += qf[e] * sv[e].y;
+                        acc[a][2] += qf[e] * sv[e].z; acc[a][3] += qf[e] * sv[e].w;
+                    }
+                }
+            }
+            // intra rows only reach columns m <= row; rows of this warp end at r8 + 7
+            for (int m0 = 0; m0 < r8 + 8; m0 += 4) {
+                float4 vn[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) vn[e] = *reinterpret_cast<const float4*>(X_s + (m0 + e) * X_LD + c4);
+#pragma unroll
+                for (int a = 0; a < 8; ++a) {
+                    const float4 in4 = *reinterpret_cast<const float4*>(Int_s + (r8 + a) * T_LD + m0);
+                    const float inv[4] = {in4.x, in4.y, in4.z, in4.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        acc2[a][0] += inv[e] * vn[e].x; acc2[a][1] += inv[e] * vn[e].y;
+                        acc2[a][2] += inv[e] * vn[e].z; acc2[a][3] += inv[e] * vn[e].w;
+                    }
+                }
+            }
+            const uint2 nwv = *reinterpret_cast<const uint2*>(norm_w + c4);
+            const float nw[4] = {lo_bf(nwv.x), hi_bf(nwv.x), lo_bf(nwv.y), hi_bf(nwv.y)};
+#pragma unroll
+            for (int a = 0; a < 8; ++a) {
+                const int r = r8 + a;
+                // o = e^cum * qinv*scale * (q~ S)  +  qinv*scale * sum_m (q~.k_m kinv_m e^(cum_r-cum_m)) v_new[m]
+                const float qs_full = qsc_s[r];
+                const float qs_nodecay = qn_s[r];
+                float o[4], ss = 0.f;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    o[b] = acc[a][b] * qs_full + acc2[a][b] * qs_nodecay;
+                    ss += o[b] * o[b];
+                }
+                ss = warp_sum(ss);
+                if (r < valid) {
+                    const float rinv = rsqrt_acc(ss * (1.0f / 128.0f) + kEps);
+                    const uint2 zv = *reinterpret_cast<const uint2*>(pr0 + (size_t)r * kGdnProjN + kOffZ + h * 128 + c4);
+                    const float z[4] = {lo_bf(zv.x), hi_bf(zv.x), lo_bf(zv.y), hi_bf(zv.y)};
+                    float out[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        float n = __fmul_rn(o[b], rinv);
+                        n = __fmul_rn(nw[b], n);
+                        out[b] = __fmul_rn(n, silu_acc(z[b]));
+                    }
+                    *reinterpret_cast<uint2*>(y + ((size_t)lane_id * T + t0 + r) * kValueDim + h * 128 + c4) =
+                        make_uint2(pack_bf2(out[0], out[1]), pack_bf2(out[2], out[3]));
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- S = e^cumC S + (k_hat e^(cumC - cum))^T v_new  (thread: 16 rows x 4 columns) ---------
+        {
+            const float cd = expf(cum_s[C - 1]);
+            const int d16 = warp * 16;
+            float acc[16][4];
+#pragma unroll
+            for (int a = 0; a < 16; ++a) {
+                const float4 s4 = *reinterpret_cast<const float4*>(S_s + (d16 + a) * 128 + c4);
+                acc[a][0] = s4.x * cd; acc[a][1] = s4.y * cd; acc[a][2] = s4.z * cd; acc[a][3] = s4.w * cd;
+            }
+            for (int i = 0; i < C; ++i) {
+                const float4 vn = *reinterpret_cast<const float4*>(X_s + i * X_LD + c4);
+                const float ks = kout_s[i];
+                float kf[16];
+                {
+                    float t8[8];
+                    unpack8f(*reinterpret_cast<const uint4*>(K_s + i * KQ_LD + d16), t8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) kf[e] = t8[e] * ks;
+                    unpack8f(*reinterpret_cast<const uint4*>(K_s + i * KQ_LD + d16 + 8), t8);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) kf[8 + e] = t8[e] * ks;
+                }
+#pragma unroll
+                for (int a = 0; a < 16; ++a) {
+                    acc[a][0] += kf[a] * vn.x; acc[a][1] += kf[a] * vn.y;
+                    acc[a][2] += kf[a] * vn.z; acc[a][3] += kf[a] * vn.w;
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < 16; ++a)
+                *reinterpret_cast<float4*>(S_s + (d16 + a) * 128 + c4) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+        }
+        __syncthreads();
+    }
+
+    for (int i = tid; i < 128 * 32; i += 256)
+        reinterpret_cast<float4*>(S_g)[i] = reinterpret_cast<const float4*>(S_s)[i];
+}
+
+}  // namespace
+
+cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
+    if (p.lanes <= 0 || p.T <= 0 || p.lanes > 65535 || p.checkpoint) return cudaErrorInvalidValue;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kChunkSmem);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    gdn_conv_prep_kernel<<<dim3(p.lanes, kConvCh / 512), 256, 0, st>>>(const_cast<uint16_t*>(p.proj), p.conv_w, p.win[0],
+                                                                  p.win[1], p.sel, p.T);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    gdn_chunk_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w, p.S[0],
+                                                                       p.S[1], p.sel, p.y, p.T);
+    return cudaGetLastError();
+}
+
+}  // namespace q35

@@ -226,6 +226,42 @@ def test_gdn_step_vs_oracle(eng, weights, lanes, T):
         assert rel_l2(y[i * T:(i + 1) * T].float(), d["y"].float()) <= 1e-2
 
 
+def test_gdn_chunked_golden(eng, weights, golden):
+    """T = 130 rows (two full chunks + a ragged one) from a zero state on the reference's own
+    inputs: the chunk-64 scan's state within 1e-4 of the reference's chunked AND recurrent forms."""
+    g = golden["stage_gdn"]
+    xT = bf(g["xT"])
+    proj = gdn_proj_rows(weights, 0, xT)
+    S0 = torch.zeros((1, 16, 128, 128))
+    win0 = torch.zeros((1, 3, 6144), dtype=torch.bfloat16)
+    y, S1, w1 = gdn_device_step(eng, weights, 0, proj.clone(), S0, win0, 1, 130)
+    e_c = rel_l2(S1[0][[0, 15]], g["ST_chunk_h"])
+    e_r = rel_l2(S1[0][[0, 15]], g["ST_rec_h"])
+    note("gdn_chunked_golden_state_vs_chunk_vs_recurrent", [e_c, e_r])
+    assert e_c <= 1e-4 and e_r <= 1e-4
+    assert np.array_equal(w1[0].float().numpy(), g["winT"])
+    mix = eng.op_linear(cu(y), cu(weights[O.LM + "layers.0.linear_attn.out_proj.weight"]))
+    assert rel_l2(mix.float().cpu(), g["mixT_chunk"]) <= 1e-2
+
+
+@pytest.mark.parametrize("lanes,T", [(2, 32), (1, 64), (3, 100), (1, 192)])
+def test_gdn_chunked_vs_oracle(eng, weights, lanes, T):
+    """Random initial state and window per lane, ragged and exact chunk counts."""
+    l = 2
+    gen = torch.Generator().manual_seed(7 * lanes + T)
+    h = torch.randn((lanes, T, 1024), generator=gen).to(torch.bfloat16)
+    win = torch.randn((lanes, 3, 6144), generator=gen).to(torch.bfloat16)
+    S0 = torch.randn((lanes, 16, 128, 128), generator=gen) * 0.1
+    proj = torch.stack([gdn_proj_rows(weights, l, h[i]) for i in range(lanes)]).reshape(lanes * T, -1)
+    y, S1, w1 = gdn_device_step(eng, weights, l, proj.clone(), S0, win, lanes, T)
+    for i in range(lanes):
+        d = {}
+        O.gdn_mixer(weights, l, h[i], win[i], S0[i], "chunk", d)
+        assert rel_l2(S1[i], d["state"]) <= 1e-4, (i, rel_l2(S1[i], d["state"]))
+        assert torch.equal(w1[i], d["window"])
+        assert rel_l2(y[i * T:(i + 1) * T].float(), d["y"].float()) <= 1e-2
+
+
 # ------------------------------------------------------------------------------------- attention
 def paged(K, V, pages_per_lane, lanes):
     """Scatter contiguous caches [lanes][ctx][2][256] into page pools + an (arbitrary) page table."""
