@@ -320,6 +320,7 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
         CK(copy_rows(e->mtp_norm_out, w->mtp.norm_out, kHidden, st));
     }
     const size_t R = (size_t)e->max_rows;
+    e->head_rows_cap = e->max_rows < 16384 ? e->max_rows : 16384;   // the head sees lanes (or 2 x lanes) rows, never a whole prefill body
     CK(dev_alloc(e->allocs, &e->resid, R * kHidden));
     CK(dev_alloc(e->allocs, &e->normed, R * kHidden));
     CK(dev_alloc(e->allocs, &e->proj, R * kGdnProjN));
@@ -329,7 +330,6 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     CK(dev_alloc(e->allocs, &e->pair, (e->has_mtp ? (size_t)e->head_rows_cap : 1) * 2048));
     CK(dev_alloc(e->allocs, &e->last_normed, R * kHidden));
     e->parts_cap = (e->vocab + 31) / 32;
-    e->head_rows_cap = e->max_rows < 16384 ? e->max_rows : 16384;   // the head sees lanes (or 2 x lanes) rows, never a whole prefill body
     CK(dev_alloc(e->allocs, &e->partials, (size_t)e->head_rows_cap * e->parts_cap));
     CK(dev_alloc(e->allocs, &e->tok2, R));
     CK(dev_alloc(e->allocs, &e->tgt, R));
@@ -689,7 +689,7 @@ extern "C" int q35_mtp_state_create(q35_engine* e, q35_state* s, int max_ctx, q3
     REQUIRE(e && s && out, Q35_ERR_ARG, "q35_mtp_state_create: null argument");
     REQUIRE(e->has_mtp, Q35_ERR_STATE, "engine was created without MTP weights");
     REQUIRE(s->e == e, Q35_ERR_STATE, "state belongs to another engine");
-    REQUIRE(2 * s->lanes <= e->max_rows, Q35_ERR_CAPACITY, "verify needs max_rows >= 2 * lanes");
+    REQUIRE(2 * s->lanes <= e->head_rows_cap, Q35_ERR_CAPACITY, "verify needs 2 * lanes <= %d head rows", e->head_rows_cap);
     REQUIRE(max_ctx >= 1 && max_ctx <= 8192, Q35_ERR_CAPACITY, "max_ctx %d out of range", max_ctx);
     q35_mtp_state* m = new q35_mtp_state();
     m->e = e; m->s = s; m->lanes = s->lanes; m->max_ctx = max_ctx;
