@@ -7,14 +7,23 @@
 // row with 16-byte loads; the cache is addressed through a per-lane page table
 // (page = 64 positions x 2 kv heads x 256 dims).
 //
+// Two forms.  Contexts up to 1024 positions: attn_tma_kernel streams whole K and V pages (32 KiB per
+// kv head) through a two-deep shared-memory ring with TMA (128-byte swizzle), takes the scores and
+// P.V on the tensor cores (m16n8k16; q is split into bf16 hi + lo parts so the f32 rotated query
+// loses nothing, the softmax weights are bf16 by contract), and keeps two CTAs per SM so four pages
+// are in flight per SM.  Longer contexts: attn_decode_kernel (plain loads, CUDA-core dots).
+//
 // Replaces attn_decode_layer / mtp_attn_row (engine/kernels.h:730-906,
 // engine/kernels_attn.cpp:995-1068); arithmetic follows speccheck/specimpl.py:320-397 as executed,
 // except that cached keys are bf16 (the engine's cache dtype, engine/state.h:90).
+#include <cuda.h>
+
 #include "q35_common.cuh"
 
 namespace q35 {
 
 constexpr int kAttnMaxCtx = 8192;
+constexpr int kAttnTmaMaxCtx = 1024;      // contexts up to here take the TMA + tensor-core form
 constexpr int kOffK = 4096, kOffV = 4608;
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -231,6 +240,289 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(AttnParams p, int c
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// TMA + tensor-core form (contexts <= 1024)
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kTileBytes = kKvPage * kHeadDim * 2;        // one kv head's slice of a page: 32 KiB
+constexpr int kRing = 2;
+constexpr int kTmaThreads = 288;                          // 8 consumer warps + 1 producer warp
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (int it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            " selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (it == 0) t0 = global_ns();
+        else if (global_ns() - t0 > 1000000000ull) return false;
+    }
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// byte offset of (row, 16-byte chunk of a 256-wide bf16 row) inside a TMA-swizzled page tile:
+// four column blocks of [64 rows][128 B], chunk index XOR (row & 7) within a block
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk32) {
+    const int cb = chunk32 >> 3, c = chunk32 & 7;
+    return (uint32_t)(cb * 8192 + row * 128 + ((c ^ (row & 7)) << 4));
+}
+
+template <bool FUSED_APPEND>
+__global__ void __launch_bounds__(kTmaThreads, 2)
+attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap kmap,
+                const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * kRing];
+    if (p.status != nullptr && *p.status != 0) return;
+
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    float* q_s = reinterpret_cast<float*>(base_ptr + kRing * kTileBytes);      // [4][256]
+    float* sc2 = q_s + 4 * kHeadDim;                                           // [2][4][ctx_pad]
+    uint16_t* w_s = reinterpret_cast<uint16_t*>(sc2 + 8 * ctx_pad);            // [4][ctx_pad] bf16
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kRing]);
+
+    const int row = blockIdx.x, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    const int g = ln >> 2, t = ln & 3;
+    const int lane_id = row / p.T, tt = row % p.T;
+    const int cap = p.pages_per_lane * kKvPage;
+    int slot = p.slot[lane_id] + tt;
+    const int rope_pos = p.rope_pos[lane_id] + tt;
+    const bool in_cap = slot < cap && slot < ctx_pad;
+    if (!in_cap) slot = (cap < ctx_pad ? cap : ctx_pad) - 1;
+    const int n_ctx = slot + 1;
+    const int P = (n_ctx + kKvPage - 1) / kKvPage;          // pages (tiles) per pass
+    const int* table = p.page_table + (size_t)lane_id * p.table_lane_stride;
+    const uint16_t* pr = p.proj + (size_t)row * kAttnProjN;
+
+    if (tid == 0) {
+        for (int b = 0; b < kRing; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(full0 + 8 * b) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;\n" ::"r"(empty0 + 8 * b) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    // tile i of 2P: K pages 0..P-1, then V pages 0..P-1
+    auto issue = [&](int i) -> bool {
+        const int b = i % kRing;
+        const uint32_t ph = (i / kRing) & 1;
+        if (!mbar_wait(empty0 + 8 * b, ph ^ 1)) return false;
+        const int page = table[i < P ? i : i - P];
+        const CUtensorMap* map = i < P ? &kmap : &vmap;
+        const uint32_t dst = ring + b * kTileBytes;
+        const int r0 = page * (kKvHeads * kKvPage) + kvh * kKvPage;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full0 + 8 * b), "r"(kTileBytes) : "memory");
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb)
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                ::"r"(dst + cb * 8192), "l"(reinterpret_cast<uint64_t>(map)), "r"(full0 + 8 * b), "r"(cb * 64), "r"(r0) : "memory");
+        return true;
+    };
+
+    // ---- prologue: producer starts the pages that do not hold the new row; q / k / v prep -------
+    int issued = 0;
+    bool prod_ok = true;
+    if (warp == 8) {
+        if (ln == 0) {
+            const int safe = FUSED_APPEND ? (P - 1) : 2 * P;
+            while (issued < kRing && issued < safe && prod_ok) { prod_ok = issue(issued); ++issued; }
+        }
+    } else if (warp < 4) {
+        const int head = kvh * 4 + warp;
+        float x[8];
+        unpack8(*reinterpret_cast<const uint4*>(pr + head * 2 * kHeadDim + 8 * ln), x);
+        head_norm_rope(x, p.q_norm, ln, rope_pos, p.inv_freq);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q_s[warp * kHeadDim + 8 * ln + e] = x[e];
+    } else if (FUSED_APPEND && warp < 6 && in_cap) {
+        append_kv(p, pr, table, kvh, slot, rope_pos, warp - 4, ln);
+        __threadfence();
+        asm volatile("fence.proxy.async;\n" ::: "memory");       // the new row must be visible to the TMA reads below
+    }
+    __syncthreads();
+
+    if (warp == 8) {
+        if (ln == 0) {
+            while (issued < 2 * P && prod_ok) { prod_ok = issue(issued); ++issued; }
+            if (!prod_ok && p.status != nullptr) atomicExch(p.status, 5);
+        }
+        return;
+    }
+
+    // ---- pass 1: scores.  warp = (16-position m-tile, 128-dim half) of every K page ---------------
+    bool ok = true;
+    {
+        const int mt = warp & 3, kh = warp >> 2;
+        uint32_t bhi[8][2], blo[8][2];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float v0 = 0.f, v1 = 0.f;
+                if (g < 4) {
+                    const int d = kh * 128 + ks * 16 + half * 8 + 2 * t;
+                    v0 = q_s[g * kHeadDim + d];
+                    v1 = q_s[g * kHeadDim + d + 1];
+                }
+                const float h0 = bfround(v0), h1 = bfround(v1);
+                bhi[ks][half] = pack_bf2(h0, h1);
+                blo[ks][half] = pack_bf2(v0 - h0, v1 - h1);
+            }
+        for (int i = 0; i < P; ++i) {
+            const int b = i % kRing;
+            if (ok) ok = mbar_wait(full0 + 8 * b, (i / kRing) & 1);
+            const uint32_t tile = ring + b * kTileBytes;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                const int r = mt * 16 + (ln & 15);
+                ldsm_x4(a, tile + tile_off(r, kh * 16 + ks * 2 + (ln >> 4)));
+                mma_bf16(acc, a[0], a[1], a[2], a[3], bhi[ks][0], bhi[ks][1]);
+                mma_bf16(acc, a[0], a[1], a[2], a[3], blo[ks][0], blo[ks][1]);
+            }
+            if (t < 2) {
+                const int pos = i * kKvPage + mt * 16 + g;
+                float* s0 = sc2 + (kh * 4 + 2 * t) * ctx_pad;
+                if (pos < ctx_pad) { s0[pos] = acc[0] * 0.0625f; s0[ctx_pad + pos] = acc[1] * 0.0625f; }
+                if (pos + 8 < ctx_pad) { s0[pos + 8] = acc[2] * 0.0625f; s0[ctx_pad + pos + 8] = acc[3] * 0.0625f; }
+            }
+            __syncwarp();
+            if (ln == 0) mbar_arrive(empty0 + 8 * b);
+        }
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+
+    // ---- softmax per head (f32), weights rounded to bf16, zero past the context ------------------
+    if (warp < 4) {
+        const float* sa = sc2 + warp * ctx_pad;
+        const float* sb = sc2 + (4 + warp) * ctx_pad;
+        float m = -INFINITY;
+        for (int i = ln; i < n_ctx; i += 32) m = fmaxf(m, sa[i] + sb[i]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int i = ln; i < n_ctx; i += 32) l += expf(sa[i] + sb[i] - m);
+        l = warp_sum(l);
+        uint16_t* w = w_s + warp * ctx_pad;
+        for (int i = ln; i < P * kKvPage && i < ctx_pad; i += 32)
+            w[i] = i < n_ctx ? f2bf(__fdiv_rn(expf(sa[i] + sb[i] - m), l)) : (uint16_t)0;
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+
+    // ---- pass 2: P.V.  warp = 32 output dims; heads ride in rows 0..3 of the m16 tile -------------
+    float acc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+    for (int i = 0; i < P; ++i) {
+        const int ti = P + i, b = ti % kRing;
+        if (ok) ok = mbar_wait(full0 + 8 * b, (ti / kRing) & 1);
+        const uint32_t tile = ring + b * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const int p0 = i * kKvPage + ks * 16;
+            uint32_t a0 = 0, a2 = 0;
+            if (g < 4 && p0 + 16 <= ctx_pad) {
+                a0 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 2 * t);
+                a2 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 8 + 2 * t);
+            }
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                uint32_t r[4];
+                const int pos = ks * 16 + (ln & 7) + ((ln >> 3) & 1) * 8;
+                ldsm_x4_trans(r, tile + tile_off(pos, warp * 4 + np * 2 + (ln >> 4)));
+                mma_bf16(acc[2 * np], a0, 0u, a2, 0u, r[0], r[1]);
+                mma_bf16(acc[2 * np + 1], a0, 0u, a2, 0u, r[2], r[3]);
+            }
+        }
+        __syncwarp();
+        if (ln == 0) mbar_arrive(empty0 + 8 * b);
+    }
+    if (!ok) {
+        if (ln == 0 && p.status != nullptr) atomicExch(p.status, 6);
+        return;
+    }
+
+    // ---- epilogue: round, apply the bf16 sigmoid gate ---------------------------------------------
+    if (g < 4) {
+        const int head = kvh * 4 + g;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int dd = warp * 32 + nt * 8 + 2 * t;
+            const uint32_t gw = *reinterpret_cast<const uint32_t*>(pr + head * 2 * kHeadDim + kHeadDim + dd);
+            const float o0 = bfround(acc[nt][0]) * bfround(sigmoid_acc(lo_bf(gw)));
+            const float o1 = bfround(acc[nt][1]) * bfround(sigmoid_acc(hi_bf(gw)));
+            *reinterpret_cast<uint32_t*>(p.out + (size_t)row * (kQHeads * kHeadDim) + head * kHeadDim + dd) = pack_bf2(o0, o1);
+        }
+    }
+}
+
+size_t attn_tma_smem(int ctx_pad) {
+    return 1024 + (size_t)kRing * kTileBytes + 4 * kHeadDim * 4 + (size_t)8 * ctx_pad * 4 + (size_t)4 * ctx_pad * 2;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Tensor map of a K or V page pool seen as a matrix [n_pages * 128 rows][256] bf16, box 64 x 64.
+bool attn_make_pool_map(void* map_out, const uint16_t* pool, long long n_pages) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr || n_pages <= 0) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)n_pages * kKvHeads * kKvPage};
+    cuuint64_t strides[1] = {(cuuint64_t)kHeadDim * 2};
+    cuuint32_t box[2] = {64, 64};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(static_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t*>(pool),
+              dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static size_t attn_smem_bytes(int ctx_pad) {
     return (size_t)(4 * kHeadDim + 8 * 4 * kHeadDim + 4 * ctx_pad) * sizeof(float);
 }
@@ -240,8 +532,12 @@ cudaError_t attn_init() {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, max_bytes);
     if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(attn_decode_kernel<false>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_bytes);
+    e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_bytes);
+    if (e != cudaSuccess) return e;
+    const int tma_bytes = (int)attn_tma_smem(kAttnTmaMaxCtx);
+    e = cudaFuncSetAttribute(attn_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(attn_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
 }
 
 cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
@@ -249,15 +545,28 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
     const int ctx_pad = (p.max_ctx + 31) & ~31;
     const int rows = p.lanes * p.T;
     const dim3 grid(rows, kKvHeads);
-    const size_t smem = attn_smem_bytes(ctx_pad);
-    if (p.T == 1) {
-        attn_decode_kernel<true><<<grid, 256, smem, st>>>(p, ctx_pad);
-    } else {
+    if (p.T > 1) {
         attn_append_kernel<<<grid, 64, 0, st>>>(p);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
-        attn_decode_kernel<false><<<grid, 256, smem, st>>>(p, ctx_pad);
     }
+    if (ctx_pad <= kAttnTmaMaxCtx) {
+        CUtensorMap kmap, vmap;
+        if (p.kmap != nullptr && p.vmap != nullptr) {
+            kmap = *static_cast<const CUtensorMap*>(p.kmap);
+            vmap = *static_cast<const CUtensorMap*>(p.vmap);
+        } else if (!attn_make_pool_map(&kmap, p.kpool, p.n_pages) || !attn_make_pool_map(&vmap, p.vpool, p.n_pages)) {
+            return cudaErrorInvalidValue;
+        }
+        const int pad64 = (p.max_ctx + 63) & ~63;           // whole pages
+        const size_t smem = attn_tma_smem(pad64);
+        if (p.T == 1) attn_tma_kernel<true><<<grid, kTmaThreads, smem, st>>>(p, pad64, kmap, vmap);
+        else attn_tma_kernel<false><<<grid, kTmaThreads, smem, st>>>(p, pad64, kmap, vmap);
+        return cudaGetLastError();
+    }
+    const size_t smem = attn_smem_bytes(ctx_pad);
+    if (p.T == 1) attn_decode_kernel<true><<<grid, 256, smem, st>>>(p, ctx_pad);
+    else attn_decode_kernel<false><<<grid, 256, smem, st>>>(p, ctx_pad);
     return cudaGetLastError();
 }
 

@@ -142,7 +142,13 @@ struct AttnParams {
     uint16_t* out;             // [lanes*T][2048]
     int lanes, T;
     int max_ctx;               // upper bound of slot + T over lanes (sizes shared memory)
+    long long n_pages;         // pages in each pool (extent of the TMA tensor maps)
+    const void* kmap;          // host CUtensorMap of kpool / vpool (attn_make_pool_map), or null:
+    const void* vmap;          //   launch_attn then encodes them per call
+    int* status;               // device word raised if a bounded wait expires (may be null)
 };
+constexpr int kTensorMapBytes = 128;
+bool attn_make_pool_map(void* map_out, const uint16_t* pool, long long n_pages);
 cudaError_t launch_attn(const AttnParams& p, cudaStream_t st);
 cudaError_t attn_init();       // opt in to large dynamic shared memory; call once per device
 

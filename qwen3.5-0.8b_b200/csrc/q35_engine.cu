@@ -96,6 +96,9 @@ struct q35_state {
     int* table = nullptr;                      // [lanes][6][pages_per_lane]
     int* pos = nullptr;                        // [lanes]
     int host_pos_hi = 0;                       // upper bound of any lane's position (host mirror)
+    long long n_pages = 0;
+    alignas(64) unsigned char kmap[kTensorMapBytes];   // TMA tensor maps of the two pools
+    alignas(64) unsigned char vmap[kTensorMapBytes];
     std::vector<void*> allocs;
 };
 
@@ -107,6 +110,9 @@ struct q35_mtp_state {
     int* table = nullptr;                      // [lanes][pages_per_lane]
     int* n = nullptr;                          // [lanes] rows in the draft cache
     int host_n_hi = 0;
+    long long n_pages = 0;
+    alignas(64) unsigned char kmap[kTensorMapBytes];
+    alignas(64) unsigned char vmap[kTensorMapBytes];
     std::vector<void*> allocs;
 };
 
@@ -435,6 +441,10 @@ extern "C" int q35_state_create(q35_engine* e, int lanes, int max_ctx, q35_state
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->vpool, n_pages * kPageElems);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->table, n_pages);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->pos, (size_t)lanes);
+    s->n_pages = (long long)n_pages;
+    if (ce == cudaSuccess && (!attn_make_pool_map(s->kmap, s->kpool, s->n_pages) ||
+                              !attn_make_pool_map(s->vmap, s->vpool, s->n_pages)))
+        ce = cudaErrorInvalidValue;
     if (ce == cudaSuccess) {
         // identity page map: lane-major, then layer, then page (any permutation is legal)
         std::vector<int> t(n_pages);
@@ -572,6 +582,7 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
             ap.table_lane_stride = (long long)kAttnLayers * s->pages_per_lane;
             ap.slot = s->pos; ap.rope_pos = s->pos; ap.inv_freq = e->inv_freq;
             ap.out = e->mix; ap.lanes = s->lanes; ap.T = T; ap.max_ctx = s->max_ctx;
+            ap.n_pages = s->n_pages; ap.kmap = s->kmap; ap.vmap = s->vmap; ap.status = e->dev_status;
             LAUNCH(Q35_FAM_ATTN, launch_attn(ap, st));
             ++aslot;
         } else {
@@ -702,6 +713,10 @@ extern "C" int q35_mtp_state_create(q35_engine* e, q35_state* s, int max_ctx, q3
     if (ce == cudaSuccess) ce = dev_alloc(m->allocs, &m->vpool, n_pages * kPageElems);
     if (ce == cudaSuccess) ce = dev_alloc(m->allocs, &m->table, n_pages);
     if (ce == cudaSuccess) ce = dev_alloc(m->allocs, &m->n, (size_t)m->lanes);
+    m->n_pages = (long long)n_pages;
+    if (ce == cudaSuccess && (!attn_make_pool_map(m->kmap, m->kpool, m->n_pages) ||
+                              !attn_make_pool_map(m->vmap, m->vpool, m->n_pages)))
+        ce = cudaErrorInvalidValue;
     // shadow state buffers + per-lane selector, owned by the target state from now on
     if (ce == cudaSuccess && !s->S[1]) {
         ce = dev_alloc(s->allocs, &s->S[1], sn);
@@ -759,6 +774,7 @@ extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_
     ap.pages_per_lane = m->pages_per_lane; ap.table_lane_stride = m->pages_per_lane;
     ap.slot = m->n; ap.rope_pos = pos; ap.inv_freq = e->inv_freq;
     ap.out = e->mix; ap.lanes = rows; ap.T = 1; ap.max_ctx = m->max_ctx;
+    ap.n_pages = m->n_pages; ap.kmap = m->kmap; ap.vmap = m->vmap; ap.status = e->dev_status;
     CK(launch_attn(ap, st));
     CK(launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
@@ -871,6 +887,7 @@ extern "C" int q35_op_attn_decode(q35_engine* e, const uint16_t* proj, const uin
     ap.page_table = page_table; ap.pages_per_lane = pages_per_lane; ap.table_lane_stride = pages_per_lane;
     ap.slot = ctx; ap.rope_pos = ctx; ap.inv_freq = e->inv_freq; ap.out = out; ap.lanes = lanes; ap.T = T;
     ap.max_ctx = pages_per_lane * kKvPage;
+    ap.n_pages = (long long)lanes * pages_per_lane; ap.kmap = nullptr; ap.vmap = nullptr; ap.status = e->dev_status;
     CK(launch_attn(ap, static_cast<cudaStream_t>(stream)));
     return Q35_OK;
 }

@@ -99,8 +99,10 @@ def test_decode_teacher_forced_from_imported_state(eng, weights, golden, prefill
             strong_ok += ok
         # lane 1 against the oracle run live (its own greedy continuation, teacher-forced by the oracle)
         nb = lane_b.forward([tok_b])
-        ref_b, _ = O.top2_margin(lane_b.logits_f32(nb)[-1])
+        ref_b, margin_b = O.top2_margin(lane_b.logits_f32(nb)[-1])
         b_agree += int(out[1]) == ref_b
+        if margin_b > 0.25:
+            assert int(out[1]) == ref_b, f"lane 1 step {s}: wide-margin token differs"
         tok_b = ref_b
     note("teacher_forced_normed_rel_l2", [max(errs_n), float(np.mean(errs_n))])
     note("teacher_forced_logits_rel_l2", [max(errs_l), float(np.mean(errs_l))])
@@ -108,7 +110,7 @@ def test_decode_teacher_forced_from_imported_state(eng, weights, golden, prefill
     assert max(errs_n) <= CASCADE and max(errs_l) <= CASCADE
     assert errs_n[0] <= 4e-2                       # first step: one pass through 24 layers
     assert strong_ok == strong                     # wide-margin steps must agree
-    assert agree >= 24 and b_agree >= 24
+    assert agree >= 20 and b_agree >= 20           # narrow-margin steps may flip under the cascade
     assert int(st.positions[0]) == 96 and int(st.positions[1]) == 96
     # GDN state after 32 steps, layer 0 (cascade-free: its inputs depend on embeddings only)
     fin = st.export_lane(0, 128)
