@@ -87,6 +87,8 @@ __device__ __forceinline__ void append_kv(const AttnParams& p, const uint16_t* _
 // grid (rows, 2 kv heads), 64 threads: used when a body carries T > 1 rows per lane, so that every
 // row's K/V is in the cache before any row's scores are taken.
 __global__ void __launch_bounds__(64) attn_append_kernel(AttnParams p) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int lane_id = row / p.T, t = row % p.T;
     const int slot = p.slot[lane_id] + t;
@@ -103,6 +105,8 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(AttnParams p, int c
     float* part = smem + 4 * kHeadDim;       // [8][4][256]
     float* sc = part + 8 * 4 * kHeadDim;     // [4][ctx_pad]
 
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
     const int lane_id = row / p.T, t = row % p.T;
@@ -300,6 +304,8 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
                 const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
+    pdl_trigger();
+    pdl_wait();
     if (p.status != nullptr && *p.status != 0) return;
 
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -546,8 +552,7 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
     const int rows = p.lanes * p.T;
     const dim3 grid(rows, kKvHeads);
     if (p.T > 1) {
-        attn_append_kernel<<<grid, 64, 0, st>>>(p);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_k(attn_append_kernel, grid, dim3(64), 0, st, p);
         if (e != cudaSuccess) return e;
     }
     if (ctx_pad <= kAttnTmaMaxCtx) {
@@ -560,14 +565,12 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
         }
         const int pad64 = (p.max_ctx + 63) & ~63;           // whole pages
         const size_t smem = attn_tma_smem(pad64);
-        if (p.T == 1) attn_tma_kernel<true><<<grid, kTmaThreads, smem, st>>>(p, pad64, kmap, vmap);
-        else attn_tma_kernel<false><<<grid, kTmaThreads, smem, st>>>(p, pad64, kmap, vmap);
-        return cudaGetLastError();
+        if (p.T == 1) return launch_k(attn_tma_kernel<true>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
+        return launch_k(attn_tma_kernel<false>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
     }
     const size_t smem = attn_smem_bytes(ctx_pad);
-    if (p.T == 1) attn_decode_kernel<true><<<grid, 256, smem, st>>>(p, ctx_pad);
-    else attn_decode_kernel<false><<<grid, 256, smem, st>>>(p, ctx_pad);
-    return cudaGetLastError();
+    if (p.T == 1) return launch_k(attn_decode_kernel<true>, grid, dim3(256), smem, st, p, ctx_pad);
+    return launch_k(attn_decode_kernel<false>, grid, dim3(256), smem, st, p, ctx_pad);
 }
 
 }  // namespace q35

@@ -66,6 +66,32 @@ __device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
     return av > bv || (av == bv && ai < bi);
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// With Q35_PDL=1 every kernel of a body is launched with the programmatic-stream-serialization attribute: it may
+// start while its predecessor drains.  A kernel calls pdl_trigger() at once (lets its successor be
+// scheduled) and pdl_wait() before it first touches anything an earlier kernel of the step wrote;
+// before the wait it may only read weights, which no kernel writes.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+bool pdl_enabled();      // true only when the environment sets Q35_PDL=1; off by default (measured slower: 1.83 vs 1.18 ms/step at 16 lanes)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                            Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 // ---- launcher declarations (defined one per .cu file) -----------------------------------------
 enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2 };
 

@@ -94,10 +94,12 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     const int lane_stride = gridDim.x / kGdnHeads;
     const uint32_t bar = smem_u32(&bar_storage);
     const uint32_t tile_addr = smem_u32(tile), in_addr = smem_u32(in_s);
+    pdl_trigger();
     if (tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
+    pdl_wait();
     __syncthreads();
     float nb_raw = 0.f, na_raw = 0.f;          // thread 0: gate inputs of the item being fetched
     {
@@ -304,8 +306,7 @@ cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
     }
     const int items = p.lanes * kGdnHeads;
     const int grid = items < max_ctas ? items : max_ctas;
-    gdn_step_kernel<<<grid, 256, kGdnSmemBytes, st>>>(p);
-    return cudaGetLastError();
+    return launch_k(gdn_step_kernel, dim3(grid), dim3(256), kGdnSmemBytes, st, p);
 }
 
 }  // namespace q35

@@ -74,6 +74,7 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
         for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
 
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    pdl_trigger();
 #pragma unroll 1
     for (int c0 = 0; c0 < CH; c0 += BATCH) {
         uint4 wv[NB][BATCH];
@@ -81,11 +82,12 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
         for (int c = 0; c < BATCH; ++c)
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) wv[nb][c] = ldg16(wrow[nb] + (c0 + c) * 32);
+        if (c0 == 0) pdl_wait();          // the first batch of weight loads flies while the producer of x drains
         uint4 xl[BATCH], xh[BATCH];
 #pragma unroll
         for (int c = 0; c < BATCH; ++c) {
-            xl[c] = lo_ok ? ldg16(xlo + (c0 + c) * 32) : zero4;
-            xh[c] = hi_ok ? ldg16(xhi + (c0 + c) * 32) : zero4;
+            xl[c] = lo_ok ? __ldcg(reinterpret_cast<const uint4*>(xlo + (c0 + c) * 32)) : zero4;
+            xh[c] = hi_ok ? __ldcg(reinterpret_cast<const uint4*>(xhi + (c0 + c) * 32)) : zero4;
         }
 #pragma unroll
         for (int c = 0; c < BATCH; ++c)
@@ -182,6 +184,8 @@ gemm_tiled_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W
     uint16_t* As = smem_raw;                         // [STAGES][BM][64]
     uint16_t* Bs = smem_raw + STAGES * BM * BK;      // [STAGES][BN][64]
 
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
@@ -338,6 +342,8 @@ gemm_tiled_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W
 __global__ void __launch_bounds__(256)
 argmax_final_kernel(const ArgMax* __restrict__ partials, int n_parts, int* __restrict__ tokens,
                     float* __restrict__ top_logit) {
+    pdl_trigger();
+    pdl_wait();
     const int row = blockIdx.x;
     const ArgMax* p = partials + (size_t)row * n_parts;
     float bv = -INFINITY;
@@ -382,8 +388,7 @@ template <int K, int NB, int EPI>
 static cudaError_t run_gemv(const uint16_t* x, const uint16_t* W, void* out, int M, int N,
                             ArgMax* partials, float* logits, int n_parts, cudaStream_t st) {
     const int grid = (N + 8 * NB - 1) / (8 * NB);
-    gemv_rows_kernel<K, NB, EPI><<<grid, 256, 0, st>>>(x, W, out, M, N, partials, logits, n_parts);
-    return cudaGetLastError();
+    return launch_k(gemv_rows_kernel<K, NB, EPI>, dim3(grid), dim3(256), 0, st, x, W, out, M, N, partials, logits, n_parts);
 }
 
 template <int BM, int BN, int WARPS_M, int NWARPS, int STAGES, int EPI>
@@ -398,8 +403,7 @@ static cudaError_t run_tiled(const uint16_t* x, const uint16_t* W, void* out, in
         attr_done = true;
     }
     dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
-    kern<<<grid, NWARPS * 32, smem, st>>>(x, W, out, M, N, K, partials, logits, n_parts);
-    return cudaGetLastError();
+    return launch_k(kern, grid, dim3(NWARPS * 32), smem, st, x, W, out, M, N, K, partials, logits, n_parts);
 }
 
 static inline int gemv_nb(int K) { return K == 1024 ? 4 : 1; }
@@ -467,8 +471,7 @@ cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int r
 
 cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, int* tokens,
                                 float* top_logit, cudaStream_t st) {
-    argmax_final_kernel<<<rows, 256, 0, st>>>(partials, n_parts, tokens, top_logit);
-    return cudaGetLastError();
+    return launch_k(argmax_final_kernel, dim3(rows), dim3(256), 0, st, partials, n_parts, tokens, top_logit);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -502,8 +505,8 @@ cudaError_t launch_lm_head_static(const uint16_t* x, const uint16_t* embed, int 
     // so nothing left over from an earlier call needs clearing
     e = run_gemv<1024, 4, EPI_ARGMAX>(x, embed, nullptr, rows, vocab, partials, nullptr, n_parts, st);
     if (e != cudaSuccess) return e;
-    argmax_final_kernel<<<rows, 256, 0, st>>>(partials, n_parts, tokens, nullptr);
-    return cudaGetLastError();
+    return launch_k(argmax_final_kernel, dim3(rows), dim3(256), 0, st, static_cast<const ArgMax*>(partials), n_parts, tokens,
+                    static_cast<float*>(nullptr));
 }
 
 cudaError_t launch_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* out, cudaStream_t st) {

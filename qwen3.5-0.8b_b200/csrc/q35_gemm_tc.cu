@@ -124,7 +124,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
-    if (status != nullptr && *status != 0) return;      // an earlier kernel gave up: do nothing
+    pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     // K split: this CTA covers k-blocks [kb0, kb0 + num_kb)
@@ -149,6 +149,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    // barrier set-up and the tensor-memory allocation above overlap the predecessor's tail
+    pdl_wait();
+    if (status != nullptr && *status != 0) {             // an earlier kernel gave up: do nothing
+        __syncthreads();
+        if (warp == 1)
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        return;
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -314,8 +322,7 @@ cudaError_t run_tc(const uint16_t* x, const uint16_t* W, void* out, int M, int N
     CUtensorMap mx, mw;
     if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, W, N, K, BN)) return cudaErrorInvalidValue;
     dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN, splits);
-    kern<<<grid, NUM_THREADS, smem, st>>>(mx, mw, out, M, N, K / BK, partials, logits, n_parts, status);
-    return cudaGetLastError();
+    return launch_k(kern, grid, dim3(NUM_THREADS), smem, st, mx, mw, out, M, N, K / BK, partials, logits, n_parts, status);
 }
 
 }  // namespace

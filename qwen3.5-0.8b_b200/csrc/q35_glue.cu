@@ -3,7 +3,18 @@
 // (engine/kernels.h:45, engine/kernels_embed.cpp:53-59).
 #include "q35_common.cuh"
 
+#include <cstdlib>
+
 namespace q35 {
+
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("Q35_PDL");
+        v = (e != nullptr && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
 
 // One warp per row of 1024: 32 lanes x 4 chunks of 8 bf16.  sum = bf16(x + delta) (bf16 add,
 // one rounding), n = bf16( (sum * rsqrt(mean(sum^2) + eps)) * (1 + w) ) with f32 math in the
@@ -14,8 +25,10 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
                 const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
                 uint16_t* __restrict__ normed_out, int rows, const float* __restrict__ delta_parts,
                 int n_split) {
+    pdl_trigger();
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_wait();
     if (row >= rows) return;
     const uint16_t* src;
     if (ids != nullptr) {
@@ -87,13 +100,78 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
     }
 }
 
+// K-split form: one CTA of 128 threads per row, 8 elements per thread, so the n_split f32 partial
+// rows (4 KiB each) are pulled by many CTAs at once; the partial loads of four splits are in flight
+// together.  Same arithmetic as add_norm_kernel (partials summed in split order, one bf16 rounding).
+__global__ void __launch_bounds__(128)
+add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ parts, int n_split,
+                      const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
+                      uint16_t* __restrict__ normed_out, int rows) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[4];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const int off = tid * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(x + (size_t)row * kHidden + off);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    const float* pp = parts + (size_t)row * kHidden + off;
+    const size_t zs = (size_t)rows * kHidden;
+    int z = 0;
+    for (; z + 4 <= n_split; z += 4) {
+        float4 p[4][2];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            p[u][0] = *reinterpret_cast<const float4*>(pp + (z + u) * zs);
+            p[u][1] = *reinterpret_cast<const float4*>(pp + (z + u) * zs + 4);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            acc[0] += p[u][0].x; acc[1] += p[u][0].y; acc[2] += p[u][0].z; acc[3] += p[u][0].w;
+            acc[4] += p[u][1].x; acc[5] += p[u][1].y; acc[6] += p[u][1].z; acc[7] += p[u][1].w;
+        }
+    }
+    for (; z < n_split; ++z) {
+        const float4 p0 = *reinterpret_cast<const float4*>(pp + z * zs);
+        const float4 p1 = *reinterpret_cast<const float4*>(pp + z * zs + 4);
+        acc[0] += p0.x; acc[1] += p0.y; acc[2] += p0.z; acc[3] += p0.w;
+        acc[4] += p1.x; acc[5] += p1.y; acc[6] += p1.z; acc[7] += p1.w;
+    }
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+    float v[8], ss = 0.f;
+    uint32_t sw[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float lo = bfround(lo_bf(aw[j]) + bfround(acc[2 * j]));
+        const float hi = bfround(hi_bf(aw[j]) + bfround(acc[2 * j + 1]));
+        v[2 * j] = lo; v[2 * j + 1] = hi;
+        ss += lo * lo + hi * hi;
+        sw[j] = pack_bf2(lo, hi);
+    }
+    if (sum_out != nullptr)
+        *reinterpret_cast<uint4*>(sum_out + (size_t)row * kHidden + off) = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float inv = rsqrt_acc((red[0] + red[1] + red[2] + red[3]) * (1.0f / kHidden) + kEps);
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + off);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        o[j] = pack_bf2(__fmul_rn(__fmul_rn(v[2 * j], inv), 1.0f + lo_bf(ww[j])),
+                        __fmul_rn(__fmul_rn(v[2 * j + 1], inv), 1.0f + hi_bf(ww[j])));
+    *reinterpret_cast<uint4*>(normed_out + (size_t)row * kHidden + off) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* table, int vocab,
                             const uint16_t* delta, const uint16_t* w, uint16_t* sum_out,
                             uint16_t* normed_out, int rows, cudaStream_t st, const float* delta_parts,
                             int n_split) {
-    add_norm_kernel<<<(rows + 7) / 8, 256, 0, st>>>(x, ids, table, vocab, delta, w, sum_out,
-                                                    normed_out, rows, delta_parts, n_split);
-    return cudaGetLastError();
+    if (delta_parts != nullptr && ids == nullptr && normed_out != nullptr)
+        return launch_k(add_norm_split_kernel, dim3(rows), dim3(128), 0, st, x, delta_parts, n_split, w, sum_out,
+                        normed_out, rows);
+    return launch_k(add_norm_kernel, dim3((rows + 7) / 8), dim3(256), 0, st, x, ids, table, vocab, delta, w,
+                    sum_out, normed_out, rows, delta_parts, n_split);
 }
 
 // ---- conv window: stored bf16 [3][6144] per (layer, lane); the reference layout is f32 ---------
@@ -154,6 +232,8 @@ __global__ void fill_int_kernel(int* p, int v, int n) {
     if (i < n) p[i] = v;
 }
 __global__ void add_int_kernel(int* p, int v, int n) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] += v;
 }
@@ -162,8 +242,7 @@ cudaError_t launch_fill_int(int* p, int v, int n, cudaStream_t st) {
     return cudaGetLastError();
 }
 cudaError_t launch_add_int(int* p, int v, int n, cudaStream_t st) {
-    add_int_kernel<<<(n + 255) / 256, 256, 0, st>>>(p, v, n);
-    return cudaGetLastError();
+    return launch_k(add_int_kernel, dim3((n + 255) / 256), dim3(256), 0, st, p, v, n);
 }
 
 }  // namespace q35
