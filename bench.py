@@ -170,7 +170,47 @@ def measure(pkg, eng, lanes: int, prompt: int, steps: int, warmup: int, dist, sa
     return dict(lanes=lanes, ms_dev=ms_dev, steps_dev=steps_dev, ms_e2e=ms_e2e, steps_e2e=steps,
                 families={k: {"ms_per_step": v[0] / steps, "launches_per_step": v[1] / steps,
                               "share": v[0] / total_ms} for k, v in fam.items()},
-                ctx_mid=ctx_mid, prefill_s=prefill_s, clocks=clocks)
+                ctx_mid=ctx_mid, prefill_s=prefill_s, clocks=clocks, last_tokens=cur.clone())
+
+
+def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warmup: int = 3) -> dict:
+    """Chunk-64 prefill of `lanes` x `prompt` ids, then `rounds` speculative rounds (MTP draft depth 1,
+    2-token verify), tokens chained on the device.  On random-init weights the draft almost never
+    matches the target, so accepted tok/s is about one token per lane per round."""
+    st = eng.allocate_state(lanes, prompt + 2 * (rounds + warmup) + 8)
+    m = eng.mtp_allocate(st, rounds + warmup + 8)
+    gen = torch.Generator().manual_seed(4000)
+    ids = torch.randint(0, eng.vocab, (lanes, prompt), generator=gen, dtype=torch.int32).cuda()
+    torch.cuda.synchronize()
+    t0 = time.time()
+    t, h = eng.prefill(st, ids, want_normed=True)
+    torch.cuda.synchronize()
+    prefill_s = time.time() - t0
+    emitted = torch.zeros((), dtype=torch.int64, device="cuda")
+
+    def one_round():
+        nonlocal t, h
+        d = eng.mtp_draft(m, h, t, (st.positions + 1).int())
+        emit, n_emit, h = eng.mtp_verify(st, m, t, d)
+        t = torch.where(n_emit == 2, emit[:, 1], emit[:, 0]).int().contiguous()
+        return n_emit
+
+    for _ in range(warmup):
+        one_round()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(rounds):
+        emitted += one_round().sum()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    n = int(emitted.item())
+    m.close()
+    st.close()
+    return {"workload": f"configs[4]: {lanes} lanes x {prompt}-token chunk-64 prefill, {rounds} rounds of MTP draft (depth 1) + 2-token verify",
+            "accepted_tok_per_s": round(n / (ms * 1e-3), 1), "accept_rate": round((n - rounds * lanes) / (rounds * lanes), 4),
+            "ms_per_round": round(ms / rounds, 4), "prefill_tok_per_s": round(lanes * prompt / prefill_s, 1)}
 
 
 def roofline_of(eng, m: dict) -> dict:
@@ -249,6 +289,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-mtp", action="store_true", help="skip the MTP (configs[4]) section")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -287,6 +328,8 @@ def main():
     eng = pkg.Engine(params, max_rows=rows)
     sampler = ClockSampler(local) if rank == 0 else None
     m = measure(pkg, eng, args.lanes, args.prompt, args.steps, args.warmup, dist, sampler)
+    # the one exchange of the data-parallel layout: sampled ids of every lane, in lane order, on rank 0
+    gathered = pkg.parallel.gather_tokens(m["last_tokens"], world * args.lanes) if dist else m["last_tokens"]
     ms_step = m["ms_dev"] / m["steps_dev"]
     value = world * args.lanes * m["steps_dev"] / (m["ms_dev"] * 1e-3)
     e2e = world * args.lanes * m["steps_e2e"] / (m["ms_e2e"] * 1e-3)
@@ -311,11 +354,16 @@ def main():
                           "frac_of_hbm_roofline": rf["step"]["frac_of_hbm_roofline"],
                           "top_kernel": rf["kernel"], "top_kernel_frac": rf["frac"],
                           "family_ms_per_step": rf["family_ms_per_step"]})
+    mtp = None
+    if rank == 0 and not args.no_mtp and eng.has_mtp:
+        mtp = measure_mtp(eng)
     if dist:
         import torch.distributed as td
         td.barrier()
     if rank == 0:
         out["lanes_sweep"] = sweep
+        out["mtp"] = mtp
+        out["gathered_token_ids"] = int(gathered.numel())
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_reference(12, 1, 1, args.prompt, params)
         print(json.dumps(out))

@@ -3,4 +3,5 @@ reference engine's step/state/prefill/MTP interface over a C-ABI CUDA library.""
 from . import weights  # noqa: F401
 from . import build as build_lib  # noqa: F401
 from . import engine  # noqa: F401
+from . import parallel  # noqa: F401
 from .engine import Engine, LaneState, MtpState, Q35Error, StepGraph, load_library  # noqa: F401
