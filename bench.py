@@ -224,6 +224,10 @@ def roofline_of(eng, m: dict) -> dict:
         nbytes = lanes * GDN_BYTES_PER_LANE_LAYER
         kernel = "gdn_step_kernel"
         traffic = GDN_NCU_TRAFFIC_PER_LANE * lanes if GDN_NCU_TRAFFIC_PER_LANE else None
+    elif top == "step_kernel":
+        nbytes = eng.step_bytes(lanes, m["ctx_mid"])
+        kernel = "small_step_kernel (whole step, persistent)"
+        traffic = None
     elif top == "head":
         nbytes = 2 * eng.vocab * 1024 + lanes * 2048
         kernel = "lm_head projection + argmax"
@@ -338,7 +342,7 @@ def main():
            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
            "e2e": {"value": round(e2e, 1), "unit": "tok/s", "h2d_bytes_per_step": 4 * args.lanes,
                    "d2h_bytes_per_step": 4 * args.lanes, "ms_per_step": round(m["ms_e2e"] / m["steps_e2e"], 5)},
-           "gpu_launches": eng.census()["launches_decode"] * m["steps_dev"],
+           "gpu_launches": eng.census()["launches_decode" if args.lanes > 16 else "launches_decode_few_lanes"] * m["steps_dev"],
            "clocks": m["clocks"], "roofline": roofline_of(eng, m), "prefill_s": round(m["prefill_s"], 2),
            "prefill_tok_per_s": round(args.lanes * args.prompt / m["prefill_s"], 1)}
     sweep = []

@@ -40,7 +40,9 @@ enum {
  * engine/decode_step.cpp:39-52) */
 enum {
     Q35_FAM_GLUE = 0, Q35_FAM_IN_PROJ = 1, Q35_FAM_GDN = 2, Q35_FAM_ATTN = 3, Q35_FAM_OUT_PROJ = 4,
-    Q35_FAM_MLP_GATEUP = 5, Q35_FAM_MLP_DOWN = 6, Q35_FAM_HEAD = 7, Q35_FAMILIES = 8
+    Q35_FAM_MLP_GATEUP = 5, Q35_FAM_MLP_DOWN = 6, Q35_FAM_HEAD = 7,
+    Q35_FAM_STEP = 8,      /* the one persistent kernel that runs a whole step at <= 16 lanes */
+    Q35_FAMILIES = 9
 };
 
 typedef struct q35_engine q35_engine;
@@ -110,7 +112,8 @@ typedef struct {
     long long lane_state_bytes;   /* per lane: GDN state read+write + conv window (f32 census) */
     long long kv_bytes_per_pos;   /* 12,288                                                 */
     long long flops_per_row;      /* matmul flops per token                                 */
-    int launches_decode;          /* kernels one q35_decode_step enqueues                   */
+    int launches_decode;          /* kernels one q35_decode_step enqueues (more than 16 lanes) */
+    int launches_decode_few_lanes;/* the same at <= 16 lanes: one persistent kernel                  */
 } q35_census;
 
 const char* q35_last_error(void);
@@ -134,6 +137,11 @@ int q35_engine_status(q35_engine* e, int* status_host);
  * milliseconds and launch counts per family (arrays of Q35_FAMILIES, host memory). */
 int q35_profile_begin(q35_engine* e);
 int q35_profile_end(q35_engine* e, double* ms_by_family, long long* launches_by_family);
+/* Phase clock of the last few-lane step taken while profiling was on (the persistent kernel has no
+ * launches to bracket): trace_host[2k] / [2k+1] = nanosecond timer of CTA 0 when it left barrier k /
+ * reached barrier k+1 (k = 0 is kernel entry); n <= 320 values.  Synchronises the device.  Replaces
+ * the per-family segments of the reference's stage_clock (engine/stage_clock.h:59-67). */
+int q35_small_step_trace(q35_engine* e, unsigned long long* trace_host, int n);
 
 /* ---- per-lane state tuple ----------------------------------------------------------------------
  * Replaces allocate_state / free_state / RequestState::reset / state_sizes

@@ -26,44 +26,6 @@ constexpr int kAttnMaxCtx = 8192;
 constexpr int kAttnTmaMaxCtx = 1024;      // contexts up to here take the TMA + tensor-core form
 constexpr int kOffK = 4096, kOffV = 4608;
 
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    f[0] = lo_bf(v.x); f[1] = hi_bf(v.x); f[2] = lo_bf(v.y); f[3] = hi_bf(v.y);
-    f[4] = lo_bf(v.z); f[5] = hi_bf(v.z); f[6] = lo_bf(v.w); f[7] = hi_bf(v.w);
-}
-
-// Zero-centred RMSNorm of one 256-wide head held 8 values per lane, then partial RoPE.
-// Returns the f32 result in x (rotated dims are NOT rounded; un-rotated dims are bf16 values).
-__device__ __forceinline__ void head_norm_rope(float (&x)[8], const uint16_t* __restrict__ w, int ln,
-                                               int rope_pos, const float* __restrict__ inv_freq) {
-    float ss = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
-    ss = warp_sum(ss);
-    const float inv = rsqrt_acc(ss * (1.0f / kHeadDim) + kEps);
-    const uint4 wv = *reinterpret_cast<const uint4*>(w + 8 * ln);
-    float wf[8];
-    unpack8(wv, wf);
-#pragma unroll
-    for (int e = 0; e < 8; ++e) x[e] = bfround(__fmul_rn(__fmul_rn(x[e], inv), 1.0f + wf[e]));
-    // lanes 0..3 hold dims 0..31, lanes 4..7 hold dims 32..63; partner of dim d is d ^ 32
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const float partner = __shfl_xor_sync(0xffffffffu, x[e], 4);
-        if (ln < 8) {
-            const int i = (8 * ln + e) & 31;
-            const float ang = __fmul_rn((float)rope_pos, inv_freq[i]);
-            const float c = cosf(ang), s = sinf(ang);
-            const float sw = ln < 4 ? -partner : partner;
-            x[e] = __fadd_rn(__fmul_rn(x[e], c), __fmul_rn(sw, s));
-        }
-    }
-}
-
-__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
-    return make_uint4(pack_bf2(f[0], f[1]), pack_bf2(f[2], f[3]), pack_bf2(f[4], f[5]),
-                      pack_bf2(f[6], f[7]));
-}
-
 __device__ __forceinline__ size_t kv_offset(const int* __restrict__ table, int pos, int kvh) {
     const int page = table[pos / kKvPage];
     return (size_t)page * kPageElems + ((size_t)kvh * kKvPage + (pos % kKvPage)) * kHeadDim;

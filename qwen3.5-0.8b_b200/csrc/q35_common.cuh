@@ -57,6 +57,47 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// ---- attention head helpers (shared by q35_attn.cu and q35_small_step.cu) ------------------------
+constexpr int kHeadDimC = 256;
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = lo_bf(v.x); f[1] = hi_bf(v.x); f[2] = lo_bf(v.y); f[3] = hi_bf(v.y);
+    f[4] = lo_bf(v.z); f[5] = hi_bf(v.z); f[6] = lo_bf(v.w); f[7] = hi_bf(v.w);
+}
+
+// Zero-centred RMSNorm of one 256-wide head held 8 values per lane, then partial RoPE.
+// Returns the f32 result in x (rotated dims are NOT rounded; un-rotated dims are bf16 values).
+__device__ __forceinline__ void head_norm_rope(float (&x)[8], const uint16_t* __restrict__ w, int ln,
+                                               int rope_pos, const float* __restrict__ inv_freq) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
+    ss = warp_sum(ss);
+    const float inv = rsqrt_acc(ss * (1.0f / kHeadDimC) + kEps);
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + 8 * ln);
+    float wf[8];
+    unpack8(wv, wf);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = bfround(__fmul_rn(__fmul_rn(x[e], inv), 1.0f + wf[e]));
+    // lanes 0..3 hold dims 0..31, lanes 4..7 hold dims 32..63; partner of dim d is d ^ 32
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float partner = __shfl_xor_sync(0xffffffffu, x[e], 4);
+        if (ln < 8) {
+            const int i = (8 * ln + e) & 31;
+            const float ang = __fmul_rn((float)rope_pos, inv_freq[i]);
+            const float c = cosf(ang), s = sinf(ang);
+            const float sw = ln < 4 ? -partner : partner;
+            x[e] = __fadd_rn(__fmul_rn(x[e], c), __fmul_rn(sw, s));
+        }
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    return make_uint4(pack_bf2(f[0], f[1]), pack_bf2(f[2], f[3]), pack_bf2(f[4], f[5]),
+                      pack_bf2(f[6], f[7]));
+}
+
+
 // (value, index) with the greedy order: larger value wins, equal values -> lower index wins.
 struct ArgMax {
     float v;
@@ -177,6 +218,39 @@ constexpr int kTensorMapBytes = 128;
 bool attn_make_pool_map(void* map_out, const uint16_t* pool, long long n_pages);
 cudaError_t launch_attn(const AttnParams& p, cudaStream_t st);
 cudaError_t attn_init();       // opt in to large dynamic shared memory; call once per device
+
+// ---- one persistent kernel per decode step for <= 16 lanes (q35_small_step.cu) -----------------
+struct SmallLayer {
+    const uint16_t *in_w, *out_w, *gu_w, *down_w, *input_norm, *post_norm;
+    const uint16_t *conv_w, *A_log, *dt_bias, *gdn_norm, *q_norm, *k_norm;
+    int in_n, attn, slot;      // slot: index among the GDN (or attention) layers
+    int pad_;
+};
+struct SmallStepParams {
+    const SmallLayer* layers;  // [24], device memory
+    const uint16_t* embed;
+    const uint16_t* final_norm;
+    int vocab, lanes;
+    const int* in_tok;
+    int* out_tok;
+    float* S;                  // [18][lanes][16][128][128]
+    uint16_t* win;             // [18][lanes][3][6144]
+    uint16_t *kpool, *vpool;
+    const int* table;          // [lanes][6][pages_per_lane]
+    int pages_per_lane;
+    int* pos;
+    const float* inv_freq;
+    uint16_t *resid;           // [2][16][1024]
+    uint16_t *delta, *proj, *mix, *act, *normed;
+    float* attn_part;          // [16][8][pages_per_lane][260]
+    ArgMax* head_part;         // [grid][16]
+    unsigned* bar;             // grid-barrier counter, zeroed before every launch
+    unsigned long long* trace; // optional [2 * 160]: CTA 0's clock when it reaches / leaves each barrier
+    int* status;
+};
+constexpr int kSmallStepMaxLanes = 16;
+constexpr int kSmallStepLaunches = 1;      // kernels per step (plus a 4-byte memset of the barrier counter)
+cudaError_t launch_small_step(const SmallStepParams& p, cudaStream_t st);
 
 // state tuple <-> reference layouts
 cudaError_t launch_window_export(const uint16_t* win, float* out, cudaStream_t st);   // [3][6144]x18 handled by caller loop

@@ -3,6 +3,7 @@
 // Interface contract: include/q35_engine.h.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -74,10 +75,17 @@ struct q35_engine {
     int *tok2 = nullptr, *tgt = nullptr;     // [max_rows] token scratch
     float* inv_freq = nullptr;
     int* dev_status = nullptr;               // raised by a kernel whose bounded wait expired
+    // few-lane persistent step kernel: device copy of the layer table and its scratch
+    SmallLayer* small_layers = nullptr;
+    uint16_t* small_resid = nullptr;         // [2][16][1024]
+    ArgMax* small_head_part = nullptr;       // [1024][16]
+    unsigned* small_bar = nullptr;
+    unsigned long long* small_trace = nullptr;   // [320] phase clock of the last traced step
     float* split_ws = nullptr;               // [kMaxSplits][kSplitMaxRows][1024] f32 K-split partials
     long long weight_bytes = 0;
     std::vector<void*> allocs;
     // optional per-family kernel timing (CUDA events on the launching stream)
+    bool small_step_enabled = false;         // Q35_SMALL_STEP=1: few-lane steps run as ONE persistent kernel (measured slower, so opt-in)
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_events;     // pairs: [2i] before, [2i+1] after
     std::vector<int> prof_family;
@@ -95,6 +103,7 @@ struct q35_state {
     uint16_t *kpool = nullptr, *vpool = nullptr;
     int* table = nullptr;                      // [lanes][6][pages_per_lane]
     int* pos = nullptr;                        // [lanes]
+    float* attn_part = nullptr;                // few-lane step kernel: [16][8][pages_per_lane][260] page partials
     int host_pos_hi = 0;                       // upper bound of any lane's position (host mirror)
     long long n_pages = 0;
     alignas(64) unsigned char kmap[kTensorMapBytes];   // TMA tensor maps of the two pools
@@ -295,6 +304,10 @@ static int pack_layer(q35_engine* e, const q35_layer_weights& w, bool attn, Pack
 
 static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights* w, cudaStream_t st) {
     e->cfg = *cfg;
+    {
+        const char* env = getenv("Q35_SMALL_STEP");
+        e->small_step_enabled = env != nullptr && env[0] == '1';
+    }
     e->vocab = cfg->vocab;
     e->max_rows = cfg->max_rows;
     e->embed = w->embed;
@@ -343,6 +356,24 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     CK(dev_alloc(e->allocs, &e->split_ws, (size_t)kMaxSplits * kSplitMaxRows * kHidden));
     CK(dev_alloc(e->allocs, &e->dev_status, (size_t)4));
     CK(cudaMemsetAsync(e->dev_status, 0, 4 * sizeof(int), st));
+    {
+        SmallLayer tbl[kLayers];
+        int gs = 0, as = 0;
+        for (int l = 0; l < kLayers; ++l) {
+            const PackedLayer& L = e->layers[l];
+            tbl[l] = SmallLayer{L.in_w, L.out_w, L.gu_w, L.down_w, L.input_norm, L.post_norm, L.conv_w, L.A_log,
+                                L.dt_bias, L.gdn_norm, L.q_norm, L.k_norm, L.in_n, L.attn ? 1 : 0,
+                                L.attn ? as++ : gs++, 0};
+        }
+        CK(dev_alloc(e->allocs, &e->small_layers, (size_t)kLayers));
+        CK(cudaMemcpyAsync(e->small_layers, tbl, sizeof(tbl), cudaMemcpyHostToDevice, st));
+        CK(cudaStreamSynchronize(st));          // tbl lives on this stack frame
+        CK(dev_alloc(e->allocs, &e->small_resid, (size_t)2 * 16 * kHidden));
+        CK(dev_alloc(e->allocs, &e->small_head_part, (size_t)1024 * 16));
+        CK(dev_alloc(e->allocs, &e->small_bar, (size_t)4));
+        CK(dev_alloc(e->allocs, &e->small_trace, (size_t)320));
+        CK(cudaMemsetAsync(e->small_trace, 0, 320 * sizeof(unsigned long long), st));
+    }
     CK(cudaMemcpyAsync(e->inv_freq, e->cfg.rope_inv_freq, 32 * sizeof(float), cudaMemcpyHostToDevice, st));
     CK(cudaStreamSynchronize(st));   // the host-side config copy above must not outlive `cfg`
     return Q35_OK;
@@ -379,6 +410,12 @@ extern "C" int q35_engine_status(q35_engine* e, int* status_host) {
     return Q35_OK;
 }
 
+extern "C" int q35_small_step_trace(q35_engine* e, unsigned long long* trace_host, int n) {
+    REQUIRE(e && trace_host && n >= 1 && n <= 320, Q35_ERR_ARG, "q35_small_step_trace: bad argument");
+    CK(cudaMemcpy(trace_host, e->small_trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    return Q35_OK;
+}
+
 extern "C" int q35_step_census(const q35_engine* e, q35_census* out) {
     REQUIRE(e && out, Q35_ERR_ARG, "q35_step_census: null argument");
     out->weight_bytes = e->weight_bytes;
@@ -390,6 +427,7 @@ extern "C" int q35_step_census(const q35_engine* e, q35_census* out) {
     params += (long long)e->vocab * kHidden;
     out->flops_per_row = 2 * params;
     out->launches_decode = 1 + kLayers * 7 + 3;
+    out->launches_decode_few_lanes = kSmallStepLaunches;
     return Q35_OK;
 }
 
@@ -441,6 +479,8 @@ extern "C" int q35_state_create(q35_engine* e, int lanes, int max_ctx, q35_state
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->vpool, n_pages * kPageElems);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->table, n_pages);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->pos, (size_t)lanes);
+    if (ce == cudaSuccess && lanes <= kSmallStepMaxLanes)
+        ce = dev_alloc(s->allocs, &s->attn_part, (size_t)16 * kQHeads * s->pages_per_lane * 260);
     s->n_pages = (long long)n_pages;
     if (ce == cudaSuccess && (!attn_make_pool_map(s->kmap, s->kpool, s->n_pages) ||
                               !attn_make_pool_map(s->vmap, s->vpool, s->n_pages)))
@@ -644,6 +684,25 @@ extern "C" int q35_decode_step(q35_engine* e, q35_state* s, const int* in_tok, i
     REQUIRE(e && s && in_tok && out_tok, Q35_ERR_ARG, "q35_decode_step: null argument");
     REQUIRE(s->e == e, Q35_ERR_STATE, "q35_decode_step: state belongs to another engine");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // Few lanes, no logits wanted, no MTP shadow buffers (a speculative session keeps decode and verify
+    // on the same kernels so that speculation stays bit-lossless): one persistent kernel does the step.
+    if (s->lanes <= kSmallStepMaxLanes && logits_f32 == nullptr && s->sel == nullptr && s->attn_part != nullptr &&
+        e->small_step_enabled) {
+        REQUIRE(s->host_pos_hi + 1 <= s->max_ctx, Q35_ERR_CAPACITY, "position %d + 1 beyond max_ctx %d", s->host_pos_hi, s->max_ctx);
+        SmallStepParams sp{};
+        sp.layers = e->small_layers; sp.embed = e->embed; sp.final_norm = e->final_norm;
+        sp.vocab = e->vocab; sp.lanes = s->lanes; sp.in_tok = in_tok; sp.out_tok = out_tok;
+        sp.S = s->S[0]; sp.win = s->win[0]; sp.kpool = s->kpool; sp.vpool = s->vpool; sp.table = s->table;
+        sp.pages_per_lane = s->pages_per_lane; sp.pos = s->pos; sp.inv_freq = e->inv_freq;
+        sp.resid = e->small_resid; sp.delta = e->delta; sp.proj = e->proj; sp.mix = e->mix; sp.act = e->act;
+        sp.normed = e->normed; sp.attn_part = s->attn_part; sp.head_part = e->small_head_part;
+        sp.bar = e->small_bar; sp.status = e->dev_status;
+        sp.trace = e->prof_on ? e->small_trace : nullptr;
+        LAUNCH(Q35_FAM_STEP, launch_small_step(sp, st));
+        if (normed) CK(copy_rows(normed, e->normed, (size_t)s->lanes * kHidden, st));
+        s->host_pos_hi += 1;
+        return Q35_OK;
+    }
     int rc = run_body(e, s, in_tok, 1, 0, st);
     if (rc != Q35_OK) return rc;
     rc = run_head(e, e->normed, s->lanes, out_tok, logits_f32, st);

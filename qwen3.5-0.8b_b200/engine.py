@@ -54,12 +54,12 @@ class StateSizes(C.Structure):
 class Census(C.Structure):
     _fields_ = [("weight_bytes", C.c_longlong), ("lane_state_bytes", C.c_longlong),
                 ("kv_bytes_per_pos", C.c_longlong), ("flops_per_row", C.c_longlong),
-                ("launches_decode", C.c_int)]
+                ("launches_decode", C.c_int), ("launches_decode_few_lanes", C.c_int)]
 
 
 EXPORTS = [
     "q35_last_error", "q35_abi_version", "q35_engine_create", "q35_engine_destroy", "q35_step_census",
-    "q35_profile_begin", "q35_profile_end", "q35_engine_status",
+    "q35_profile_begin", "q35_profile_end", "q35_engine_status", "q35_small_step_trace",
     "q35_state_sizes_of", "q35_state_create", "q35_state_destroy", "q35_state_reset",
     "q35_state_positions", "q35_state_note_advance", "q35_state_export_lane", "q35_state_import_lane",
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
@@ -273,6 +273,12 @@ class Engine:
         self.embed = dev[W.LM + "embed_tokens.weight"]
         del dev
 
+    def small_step_trace(self, n: int = 320):
+        """Nanosecond clock of CTA 0 at every barrier of the last profiled few-lane step."""
+        buf = (C.c_ulonglong * n)()
+        _check(self.lib.q35_small_step_trace(self.handle, buf, n))
+        return list(buf)
+
     def status(self) -> int:
         """0 when healthy; non-zero when a kernel's bounded wait expired (synchronises the device)."""
         v = C.c_int(0)
@@ -291,15 +297,15 @@ class Engine:
         c = self.census()
         return c["weight_bytes"] + lanes * (c["lane_state_bytes"] + c["kv_bytes_per_pos"] * (ctx + 1))
 
-    FAMILIES = ["glue", "in_proj", "gdn", "attn", "out_proj", "mlp_gateup", "mlp_down", "head"]
+    FAMILIES = ["glue", "in_proj", "gdn", "attn", "out_proj", "mlp_gateup", "mlp_down", "head", "step_kernel"]
 
     def profile_begin(self):
         _check(self.lib.q35_profile_begin(self.handle))
 
     def profile_end(self) -> dict:
         """{family: (milliseconds, launches)} of every kernel launched since profile_begin."""
-        ms = (C.c_double * 8)()
-        n = (C.c_longlong * 8)()
+        ms = (C.c_double * len(self.FAMILIES))()
+        n = (C.c_longlong * len(self.FAMILIES))()
         _check(self.lib.q35_profile_end(self.handle, ms, n))
         return {f: (ms[i], n[i]) for i, f in enumerate(self.FAMILIES)}
 

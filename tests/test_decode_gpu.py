@@ -211,6 +211,46 @@ def test_determinism_lane_independence_and_graph(eng, pkg, golden):
     assert torch.equal(t1, t4) and p1 == [72, 72, 72] and p4 == [76, 76, 76]
 
 
+@pytest.mark.parametrize("lanes", [1, 3, 16])
+def test_small_step_kernel_matches_multi_kernel_path(pkg, weights, golden, monkeypatch, lanes):
+    """At <= 16 lanes one persistent kernel runs the whole step.  Against the multi-kernel path on the
+    same prompts: same positions, final-norm rows within the cascade band (the two paths sum their
+    dot products in different orders), same GDN state in layer 0 to 1e-3, and mostly equal tokens."""
+    g = golden["config0_greedy"]
+    gen = torch.Generator().manual_seed(31 + lanes)
+    ids = torch.randint(0, 248320, (lanes, 70), generator=gen).int()
+    ids[0, :64] = torch.from_numpy(g["prompt"]).int()
+    ids = ids.cuda()
+    outs = {}
+    for mode in ("0", "1"):               # the multi-kernel run goes first; its tokens are fed to both
+        monkeypatch.setenv("Q35_SMALL_STEP", mode)
+        e = pkg.Engine(weights, max_rows=2048)
+        st = e.allocate_state(lanes, 128)
+        y0, _ = e.prefill(st, ids)
+        toks, rows = [y0.clone()], []
+        cur = y0
+        for _ in range(6):
+            nrm = torch.empty((lanes, 1024), dtype=torch.bfloat16, device="cuda")
+            feed = cur if mode == "0" else outs["0"]["toks"][len(toks) - 1].cuda()
+            cur = e.decode_step(st, feed, normed=nrm)
+            toks.append(cur.clone())
+            rows.append(nrm.float().cpu())
+        outs[mode] = dict(toks=torch.stack(toks).cpu(), rows=torch.stack(rows), pos=st.positions.tolist(),
+                          S=st.export_lane(0, 128)["gdn_state"][0].cpu(), status=e.status())
+        st.close()
+        e.close()
+    a, b = outs["1"], outs["0"]
+    assert a["status"] == 0 and b["status"] == 0
+    assert a["pos"] == b["pos"] == [76] * lanes
+    assert torch.equal(a["toks"][0], b["toks"][0])
+    same = (a["toks"] == b["toks"]).float().mean().item()
+    first = rel_l2(a["rows"][0], b["rows"][0])
+    note(f"small_step_vs_multi_kernel_lanes{lanes}", [first, rel_l2(a["rows"], b["rows"]), same, rel_l2(a["S"], b["S"])])
+    assert first <= 5e-2 and rel_l2(a["rows"], b["rows"]) <= CASCADE
+    assert rel_l2(a["S"], b["S"]) <= 5e-3
+    assert same >= 0.6
+
+
 def test_host_error_paths(eng, pkg):
     st = eng.allocate_state(2, 64)
     ids = torch.zeros((2, 65), dtype=torch.int32, device="cuda")

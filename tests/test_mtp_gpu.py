@@ -56,6 +56,7 @@ def test_rounds_equal_plain_greedy_and_sequential_state(eng, golden):
     ids = prompts(golden, lanes)
     # plain greedy
     sp = eng.allocate_state(lanes, 64)
+    mp = eng.mtp_allocate(sp, 64)          # a speculative session: decode and verify share kernels
     y0, _ = eng.prefill(sp, ids)
     plain = [y0.clone()]
     cur = y0
@@ -98,13 +99,14 @@ def test_rounds_equal_plain_greedy_and_sequential_state(eng, golden):
             break
         common += 1
     assert common >= 1
-    m.close(); ss.close(); sp.close()
+    m.close(); mp.close(); ss.close(); sp.close()
 
 
 def test_accept_and_reject_branches(eng, golden):
     lanes = 2
     ids = prompts(golden, lanes)
     sp = eng.allocate_state(lanes, 64)
+    mp = eng.mtp_allocate(sp, 64)          # keeps the plain run on the kernels the verify body uses
     y0, _ = eng.prefill(sp, ids)
     seq = [y0.clone()]
     for _ in range(4):
@@ -139,7 +141,7 @@ def test_accept_and_reject_branches(eng, golden):
     assert a0["prefix_len"] == b0["prefix_len"] == 20
     assert torch.equal(a0["gdn_state"], b0["gdn_state"]) and torch.equal(a0["conv_window"], b0["conv_window"])
     assert int(nxt[0]) == int(seq[4][0])
-    m.close(); ss.close(); sp.close()
+    m.close(); mp.close(); ss.close(); sp.close()
 
 
 def test_verify_needs_mtp_state(eng, pkg, golden):
