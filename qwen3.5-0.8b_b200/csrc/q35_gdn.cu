@@ -14,6 +14,8 @@
 //
 // Replaces gdn_conv / gdn_gates / gdn_rec / gdn_gated_norm (engine/kernels.h:398-460,682);
 // arithmetic follows speccheck/specimpl.py:252-305 as executed.
+#include <cstdlib>
+
 #include "q35_common.cuh"
 
 namespace q35 {
@@ -60,8 +62,8 @@ constexpr size_t kGdnSmemBytes = kTileBytes + kInBytes;
 __device__ __forceinline__ void item_fetch(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
                                            uint32_t in_addr, uint32_t bar) {
     const int sel = p.sel != nullptr ? (p.sel[lane_id] & 1) : 0;
-    const float* S = p.S[sel] + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
-    const uint16_t* win = p.win[sel] + (size_t)lane_id * 3 * kConvCh;
+    const float* S = (sel ? p.S[1] : p.S[0]) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
+    const uint16_t* win = (sel ? p.win[1] : p.win[0]) + (size_t)lane_id * 3 * kConvCh;
     const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
@@ -85,7 +87,6 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     __shared__ __align__(16) float red_r[8][128];
     __shared__ __align__(16) float red_o[8][128];
     __shared__ float ssum[4][2];
-    __shared__ float osum[4];
     __shared__ float scal_s[2];
 
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
@@ -118,7 +119,6 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     const float q_scale = 0.08838834764831845f;   // 128^-1/2
     float tap[3][4];
     int ch[3] = {0, 0, 0};
-    float nw = 0.f;
     if (tid < 128) {
 #pragma unroll
         for (int kind = 0; kind < 3; ++kind) {
@@ -127,7 +127,11 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
             tap[kind][0] = lo_bf(tw.x); tap[kind][1] = hi_bf(tw.x);
             tap[kind][2] = lo_bf(tw.y); tap[kind][3] = hi_bf(tw.y);
         }
-        nw = bf2f(p.norm_w[tid]);
+    }
+    float nw4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (warp == 0) {
+        const uint2 nv = *reinterpret_cast<const uint2*>(p.norm_w + 4 * ln);
+        nw4[0] = lo_bf(nv.x); nw4[1] = hi_bf(nv.x); nw4[2] = lo_bf(nv.y); nw4[3] = hi_bf(nv.y);
     }
 
     uint32_t phase = 0;
@@ -135,8 +139,8 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
         const int sel = p.sel != nullptr ? (p.sel[lane_id] & 1) : 0;
         const size_t s_off = ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
         const size_t w_off = (size_t)lane_id * 3 * kConvCh;
-        float* S_live = p.S[sel] + s_off;
-        uint16_t* win_live = p.win[sel] + w_off;
+        float* S_live = (sel ? p.S[1] : p.S[0]) + s_off;
+        uint16_t* win_live = (sel ? p.win[1] : p.win[0]) + w_off;
 
         // ---- prefetched tile and inputs: shared memory -> registers ------------------------------
         if (!mbar_wait_bounded(bar, phase)) {
@@ -150,7 +154,9 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 #pragma unroll
             for (int r = 0; r < 16; ++r) s[r] = Sp[(warp * 16 + r) * 32 + ln];
         }
-        float raw0[3] = {0.f, 0.f, 0.f}, win[3][3], z0 = 0.f;
+        float raw0[3] = {0.f, 0.f, 0.f}, win[3][3];
+        uint2 z4 = make_uint2(0, 0);
+        if (warp == 0) z4 = *reinterpret_cast<const uint2*>(in_s + 12 * 128 + 4 * ln);
         if (tid < 128) {
 #pragma unroll
             for (int kind = 0; kind < 3; ++kind) {
@@ -158,7 +164,6 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 #pragma unroll
                 for (int j = 0; j < 3; ++j) win[kind][j] = bf2f(in_s[(3 + j * 3 + kind) * 128 + tid]);
             }
-            z0 = bf2f(in_s[12 * 128 + tid]);
         }
         if (tid == 0) { scal_s[0] = nb_raw; scal_s[1] = na_raw; }
         __syncthreads();                   // every thread has its copy: the buffers are free again
@@ -245,29 +250,39 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
             __syncthreads();
 
             // ---- gated RMSNorm over the head's 128 outputs (f32 until the single bf16 cast) ----
-            float o = 0.f;
-            if (tid < 128) {
+            // warp 0 alone: a lane takes 4 columns, so the mean square needs no block barrier and the
+            // other warps move on to their state stores / the next item
+            if (warp == 0) {
+                float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                for (int w = 0; w < 8; ++w) o += red_o[w][tid];
-                const float oo = warp_sum(o * o);
-                if (ln == 0) osum[warp] = oo;
-            }
-            __syncthreads();
-            if (tid < 128) {
-                const float ms = (osum[0] + osum[1] + osum[2] + osum[3]) * (1.0f / 128.0f);
-                float n = __fmul_rn(o, rsqrt_acc(ms + kEps));
-                n = __fmul_rn(nw, n);
-                const float z = (t == 0) ? z0 : bf2f(pr[kOffZ + h * 128 + tid]);
-                p.y[row * kValueDim + h * 128 + tid] = f2bf(__fmul_rn(n, silu_acc(z)));
+                for (int w = 0; w < 8; ++w) {
+                    const float4 a = *reinterpret_cast<const float4*>(&red_o[w][4 * ln]);
+                    o4.x += a.x; o4.y += a.y; o4.z += a.z; o4.w += a.w;
+                }
+                const float ms = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w) * (1.0f / 128.0f);
+                const float rinv = rsqrt_acc(ms + kEps);
+                uint2 zr = z4;
+                if (t > 0) zr = *reinterpret_cast<const uint2*>(pr + kOffZ + h * 128 + 4 * ln);
+                const float zf[4] = {lo_bf(zr.x), hi_bf(zr.x), lo_bf(zr.y), hi_bf(zr.y)};
+                const float of[4] = {o4.x, o4.y, o4.z, o4.w};
+                float out[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    float n = __fmul_rn(of[c], rinv);
+                    n = __fmul_rn(nw4[c], n);
+                    out[c] = __fmul_rn(n, silu_acc(zf[c]));
+                }
+                *reinterpret_cast<uint2*>(p.y + row * kValueDim + h * 128 + 4 * ln) =
+                    make_uint2(pack_bf2(out[0], out[1]), pack_bf2(out[2], out[3]));
             }
 
             // ---- checkpoint after the first of two tokens (speculative verify) -----------------
             if (p.checkpoint && t == 0) {
-                float4* Sc = reinterpret_cast<float4*>(p.S[sel ^ 1] + s_off);
+                float4* Sc = reinterpret_cast<float4*>((sel ? p.S[0] : p.S[1]) + s_off);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) Sc[(warp * 16 + r) * 32 + ln] = s[r];
                 if (tid < 128) {
-                    uint16_t* wc = p.win[sel ^ 1] + w_off;
+                    uint16_t* wc = (sel ? p.win[0] : p.win[1]) + w_off;
 #pragma unroll
                     for (int kind = 0; kind < 3; ++kind)
 #pragma unroll
@@ -301,7 +316,9 @@ cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(gdn_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGdnSmemBytes);
         if (e != cudaSuccess) return e;
-        max_ctas = (2 * sms / kGdnHeads) * kGdnHeads;      // two CTAs per SM, rounded down to whole lanes
+        int per_sm = 2;
+        if (const char* env = std::getenv("Q35_GDN_CTAS_PER_SM")) per_sm = env[0] == '1' ? 1 : 2;   // tuning knob
+        max_ctas = (per_sm * sms / kGdnHeads) * kGdnHeads;  // two CTAs per SM, rounded down to whole lanes
         if (max_ctas < kGdnHeads) max_ctas = kGdnHeads;
     }
     const int items = p.lanes * kGdnHeads;
