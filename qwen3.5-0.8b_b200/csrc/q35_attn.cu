@@ -49,7 +49,6 @@ __device__ __forceinline__ void append_kv(const AttnParams& p, const uint16_t* _
 // grid (rows, 2 kv heads), 64 threads: used when a body carries T > 1 rows per lane, so that every
 // row's K/V is in the cache before any row's scores are taken.
 __global__ void __launch_bounds__(64) attn_append_kernel(AttnParams p) {
-    pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int lane_id = row / p.T, t = row % p.T;
@@ -67,7 +66,6 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(AttnParams p, int c
     float* part = smem + 4 * kHeadDim;       // [8][4][256]
     float* sc = part + 8 * 4 * kHeadDim;     // [4][ctx_pad]
 
-    pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
@@ -266,7 +264,6 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
                 const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
-    pdl_trigger();
     pdl_wait();
     if (p.status != nullptr && *p.status != 0) return;
 

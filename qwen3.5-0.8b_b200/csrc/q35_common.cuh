@@ -109,13 +109,16 @@ __device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
 
 // ---- programmatic dependent launch ---------------------------------------------------------------
 // With Q35_PDL=1 every kernel of a body is launched with the programmatic-stream-serialization attribute: it may
-// start while its predecessor drains.  A kernel calls pdl_trigger() at once (lets its successor be
-// scheduled) and pdl_wait() before it first touches anything an earlier kernel of the step wrote;
-// before the wait it may only read weights, which no kernel writes.
+// start while its predecessor drains.  A kernel calls pdl_wait() before it first touches anything an
+// earlier kernel of the step wrote; before the wait it may only read what no kernel of the step
+// writes (weights; the GDN state of the previous step).  pdl_trigger() comes LATE - once the kernel
+// has issued its last loads, and always after its own wait - so at most one successor is resident
+// beside its predecessor and everything older than the predecessor is complete.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-bool pdl_enabled();      // true only when the environment sets Q35_PDL=1; off by default (measured slower: 1.83 vs 1.18 ms/step at 16 lanes)
+bool pdl_enabled();            // Q35_PDL=1/0 forces; unset: on for bodies of few rows (pdl_set_rows)
+void pdl_set_rows(int rows);   // the engine announces the row count of the body it is about to launch
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,

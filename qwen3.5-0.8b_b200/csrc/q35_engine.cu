@@ -607,6 +607,7 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
     const int rows = s->lanes * T;
     REQUIRE(rows <= e->max_rows, Q35_ERR_CAPACITY, "body of %d rows exceeds engine max_rows %d", rows, e->max_rows);
     REQUIRE(s->host_pos_hi + T <= s->max_ctx, Q35_ERR_CAPACITY, "position %d + %d beyond max_ctx %d", s->host_pos_hi, T, s->max_ctx);
+    pdl_set_rows(rows);
     LAUNCH(Q35_FAM_GLUE, launch_add_norm(nullptr, ids, e->embed, e->vocab, nullptr, e->layers[0].input_norm,
                                          e->resid, e->normed, rows, st));
     int gslot = 0, aslot = 0;

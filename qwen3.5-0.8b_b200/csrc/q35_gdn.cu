@@ -59,23 +59,33 @@ constexpr size_t kGdnSmemBytes = kTileBytes + kInBytes;
 
 // One thread: everything item (lane_id, h) needs from HBM for its first token, as bulk copies that
 // complete on one mbarrier: the 64 KiB state tile and thirteen 256-byte rows of small inputs.
-__device__ __forceinline__ void item_fetch(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
-                                           uint32_t in_addr, uint32_t bar) {
+// Two parts: the state tile and conv window (written by this layer's previous step only) and the
+// rows of this step's projection; the first may be issued before the projection kernel has ended.
+__device__ __forceinline__ void item_fetch_state(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
+                                                 uint32_t in_addr, uint32_t bar) {
     const int sel = p.sel != nullptr ? (p.sel[lane_id] & 1) : 0;
     const float* S = (sel ? p.S[1] : p.S[0]) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
     const uint16_t* win = (sel ? p.win[1] : p.win[0]) + (size_t)lane_id * 3 * kConvCh;
-    const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
     bulk_g2s(tile_addr, S, kTileBytes, bar);
 #pragma unroll
-    for (int kind = 0; kind < 3; ++kind) {
-        bulk_g2s(in_addr + kind * 256, pr + kind * 2048 + h * 128, 256, bar);
+    for (int kind = 0; kind < 3; ++kind)
 #pragma unroll
         for (int j = 0; j < 3; ++j)
             bulk_g2s(in_addr + (3 + j * 3 + kind) * 256, win + j * kConvCh + kind * 2048 + h * 128, 256, bar);
-    }
+}
+__device__ __forceinline__ void item_fetch_rows(const GdnParams& p, int lane_id, int h, uint32_t in_addr,
+                                                uint32_t bar) {
+    const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
+#pragma unroll
+    for (int kind = 0; kind < 3; ++kind) bulk_g2s(in_addr + kind * 256, pr + kind * 2048 + h * 128, 256, bar);
     bulk_g2s(in_addr + 12 * 256, pr + kOffZ + h * 128, 256, bar);
+}
+__device__ __forceinline__ void item_fetch(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
+                                           uint32_t in_addr, uint32_t bar) {
+    item_fetch_state(p, lane_id, h, tile_addr, in_addr, bar);
+    item_fetch_rows(p, lane_id, h, in_addr, bar);
 }
 
 __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
@@ -95,18 +105,19 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     const int lane_stride = gridDim.x / kGdnHeads;
     const uint32_t bar = smem_u32(&bar_storage);
     const uint32_t tile_addr = smem_u32(tile), in_addr = smem_u32(in_s);
-    pdl_trigger();
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    pdl_wait();
-    __syncthreads();
     float nb_raw = 0.f, na_raw = 0.f;          // thread 0: gate inputs of the item being fetched
     {
+        // the first state tile is on its way before the projection kernel ahead of this one has ended
         const int l0 = blockIdx.x / kGdnHeads;
+        if (tid == 0) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            if (l0 < p.lanes) item_fetch_state(p, l0, h, tile_addr, in_addr, bar);
+        }
+        pdl_wait();
+        __syncthreads();
         if (tid == 0 && l0 < p.lanes) {
-            item_fetch(p, l0, h, tile_addr, in_addr, bar);
+            item_fetch_rows(p, l0, h, in_addr, bar);
             const uint16_t* pr0 = p.proj + (size_t)l0 * p.T * kGdnProjN;
             nb_raw = bf2f(pr0[kOffB + h]);
             na_raw = bf2f(pr0[kOffA + h]);
@@ -174,6 +185,8 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
                 const uint16_t* prn = p.proj + (size_t)nxt * p.T * kGdnProjN;
                 nb_raw = bf2f(prn[kOffB + h]);
                 na_raw = bf2f(prn[kOffA + h]);
+            } else {
+                pdl_trigger();             // last item of this CTA: the next kernel may start its weight loads
             }
         }
 

@@ -74,7 +74,6 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
         for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
 
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
-    pdl_trigger();
 #pragma unroll 1
     for (int c0 = 0; c0 < CH; c0 += BATCH) {
         uint4 wv[NB][BATCH];
@@ -99,6 +98,7 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
                 mma16816(acc[nb], xl[c].z, xh[c].z, xl[c].w, xh[c].w, wv[nb][c].z, wv[nb][c].w);
             }
     }
+    pdl_trigger();          // all loads are done: the successor may start fetching its weights
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
         red[warp][g][nb * 8 + 2 * t] = acc[nb][0];
@@ -184,7 +184,6 @@ gemm_tiled_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W
     uint16_t* As = smem_raw;                         // [STAGES][BM][64]
     uint16_t* Bs = smem_raw + STAGES * BM * BK;      // [STAGES][BN][64]
 
-    pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -342,7 +341,6 @@ gemm_tiled_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W
 __global__ void __launch_bounds__(256)
 argmax_final_kernel(const ArgMax* __restrict__ partials, int n_parts, int* __restrict__ tokens,
                     float* __restrict__ top_logit) {
-    pdl_trigger();
     pdl_wait();
     const int row = blockIdx.x;
     const ArgMax* p = partials + (size_t)row * n_parts;

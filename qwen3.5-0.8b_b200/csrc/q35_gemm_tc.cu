@@ -16,6 +16,8 @@
 // skips its stores, still frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "q35_common.cuh"
 
 namespace q35 {
@@ -110,6 +112,76 @@ __device__ __forceinline__ uint16_t swiglu_bf16(float gate_acc, float up_acc) {
     return f2bf(s * u);
 }
 
+// Epilogue of 32 accumulator columns [col0, col0 + 32) of one output row, from registers.
+// PARTIAL: f32 partial tile of K split `split`; PLAIN: bf16; SWIGLU: interleaved (gate, up) pairs ->
+// bf16 activations; ARGMAX: running (value, lowest index) plus optional f32 logits.
+template <int EPI>
+__device__ __forceinline__ void epi_chunk(const uint32_t (&r)[32], void* __restrict__ out, float* __restrict__ logits,
+                                          int M, int N, int row, int col0, int split, float& bv, int& bi) {
+    const int valid = (N - col0) < 32 ? (N - col0) : 32;
+    if (EPI == EPI_PARTIAL) {
+        float* o = static_cast<float*>(out) + ((size_t)split * M + row) * N + col0;
+        if (valid == 32) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(o)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) o[j] = __uint_as_float(r[j]);
+        }
+    } else if (EPI == EPI_PLAIN) {
+        uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * N + col0;
+        if (valid == 32) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint4 w;
+                w.x = pack_bf2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                w.y = pack_bf2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                w.z = pack_bf2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                w.w = pack_bf2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                reinterpret_cast<uint4*>(o)[v] = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) o[j] = f2bf(__uint_as_float(r[j]));
+        }
+    } else if (EPI == EPI_SWIGLU) {
+        uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * (N >> 1) + (col0 >> 1);
+        if (valid == 32) {
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int b = 16 * v + 4 * j;
+                    w[j] = (uint32_t)swiglu_bf16(__uint_as_float(r[b]), __uint_as_float(r[b + 1])) |
+                           ((uint32_t)swiglu_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3])) << 16);
+                }
+                reinterpret_cast<uint4*>(o)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (2 * j + 1 < valid)
+                    o[j] = swiglu_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float v = __uint_as_float(r[j]);
+            if (j < valid && v > bv) { bv = v; bi = col0 + j; }      // ascending scan: lowest id on ties
+        }
+        if (logits != nullptr) {
+            float* lg = logits + (size_t)row * N + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < valid) lg[j] = __uint_as_float(r[j]);
+        }
+    }
+}
+
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
@@ -124,13 +196,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
-    pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     // K split: this CTA covers k-blocks [kb0, kb0 + num_kb)
     const int kb_per = (num_kb_total + gridDim.z - 1) / gridDim.z;
     const int kb0 = blockIdx.z * kb_per;
     const int num_kb = (num_kb_total - kb0) < kb_per ? (num_kb_total - kb0) : kb_per;
+    const int pre = num_kb < STAGES ? num_kb : STAGES;                 // stages filled before the first wait
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;      // 1024-byte aligned ring
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]), accum = smem_u32(&bars[2 * STAGES]);
 
@@ -139,6 +211,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
         mbar_init(accum, 1);
         abort_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // weight tiles of the first stages: no kernel writes weights, so these loads may fly while
+        // the kernel that produces x is still running
+        for (int kb = 0; kb < pre; ++kb) {
+            mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
+            tma_load_2d(tiles + kb * STAGE_BYTES + A_BYTES, &tma_w, (kb0 + kb) * BK, n0, full0 + 8 * kb);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
@@ -149,18 +227,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
-    // barrier set-up and the tensor-memory allocation above overlap the predecessor's tail
+    // barrier set-up, the tensor-memory allocation and the weight loads above overlap the predecessor's tail
     pdl_wait();
-    if (status != nullptr && *status != 0) {             // an earlier kernel gave up: do nothing
-        __syncthreads();
-        if (warp == 1)
-            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
-        return;
-    }
+    // an earlier kernel gave up: move no data beyond the loads already in flight, compute nothing
+    const bool dead = status != nullptr && *status != 0;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = 0; kb < pre; ++kb)
+                tma_load_2d(tiles + kb * STAGE_BYTES, &tma_x, (kb0 + kb) * BK, m0, full0 + 8 * kb);
+            for (int kb = pre; kb < num_kb && !dead; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { abort_s = 1; if (status) atomicExch(status, 2); break; }
@@ -169,14 +245,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
                 tma_load_2d(a, &tma_x, (kb0 + kb) * BK, m0, full0 + 8 * s);
                 tma_load_2d(a + A_BYTES, &tma_w, (kb0 + kb) * BK, n0, full0 + 8 * s);
             }
+            pdl_trigger();               // every load of this CTA is issued: the successor may start
         }
     } else if (warp == 1) {
         if (lane == 0) {
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
+            const int n_wait = dead ? pre : num_kb;      // a dead CTA still lets its own copies land
+            for (int kb = 0; kb < n_wait && ok; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!mbar_wait(full0 + 8 * s, ph)) { abort_s = 1; if (status) atomicExch(status, 3); ok = false; break; }
+                if (dead) continue;
                 tc_fence_after();
                 const uint32_t a = tiles + s * STAGE_BYTES;
 #pragma unroll
@@ -185,12 +264,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
                            (kb | k) != 0 ? 1u : 0u);
                 tc_commit(empty0 + 8 * s);       // frees the stage once these MMAs have read it
             }
-            if (ok) tc_commit(accum);            // accumulator complete
+            if (ok && !dead) tc_commit(accum);   // accumulator complete
         }
     } else {
         // ---- epilogue: thread = output row (TMEM lane), registers = columns ----------------------
-        const bool ready = mbar_wait(accum, 0);
-        if (!ready && lane == 0 && status) atomicExch(status, 4);
+        const bool ready = __all_sync(0xffffffffu, !dead && mbar_wait(accum, 0));
+        if (!ready && !dead && lane == 0 && status) atomicExch(status, 4);
         tc_fence_after();
         const int q = warp & 3;                                  // TMEM lane quarter this warp may read
         const int row = m0 + q * 32 + lane;
@@ -203,68 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
                 tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + c * 32, r);
                 const int col0 = n0 + c * 32;
                 if (row >= M || col0 >= N) continue;
-                const int valid = (N - col0) < 32 ? (N - col0) : 32;
-                if (EPI == EPI_PARTIAL) {
-                    float* o = static_cast<float*>(out) + ((size_t)blockIdx.z * M + row) * N + col0;
-                    if (valid == 32) {
-#pragma unroll
-                        for (int v = 0; v < 8; ++v)
-                            reinterpret_cast<uint4*>(o)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) o[j] = __uint_as_float(r[j]);
-                    }
-                } else if (EPI == EPI_PLAIN) {
-                    uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * N + col0;
-                    if (valid == 32) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 w;
-                            w.x = pack_bf2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            w.y = pack_bf2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            w.z = pack_bf2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            w.w = pack_bf2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            reinterpret_cast<uint4*>(o)[v] = w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) o[j] = f2bf(__uint_as_float(r[j]));
-                    }
-                } else if (EPI == EPI_SWIGLU) {
-                    uint16_t* o = static_cast<uint16_t*>(out) + (size_t)row * (N >> 1) + (col0 >> 1);
-                    if (valid == 32) {
-#pragma unroll
-                        for (int v = 0; v < 2; ++v) {
-                            uint32_t w[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int b = 16 * v + 4 * j;
-                                w[j] = (uint32_t)swiglu_bf16(__uint_as_float(r[b]), __uint_as_float(r[b + 1])) |
-                                       ((uint32_t)swiglu_bf16(__uint_as_float(r[b + 2]), __uint_as_float(r[b + 3])) << 16);
-                            }
-                            reinterpret_cast<uint4*>(o)[v] = make_uint4(w[0], w[1], w[2], w[3]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            if (2 * j + 1 < valid)
-                                o[j] = swiglu_bf16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float v = __uint_as_float(r[j]);
-                        if (j < valid && v > bv) { bv = v; bi = col0 + j; }      // ascending scan: lowest id on ties
-                    }
-                    if (logits != nullptr) {
-                        float* lg = logits + (size_t)row * N + col0;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < valid) lg[j] = __uint_as_float(r[j]);
-                    }
-                }
+                epi_chunk<EPI>(r, out, logits, M, N, row, col0, blockIdx.z, bv, bi);
             }
             if (EPI == EPI_ARGMAX && row < M) partials[(size_t)row * n_parts + blockIdx.y] = ArgMax{bv, bi};
         }
@@ -275,6 +293,194 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Persistent form for bodies with about a wave of tiles or more: one CTA per SM walks 128 x 256 output
+// tiles (row tile fastest, so the CTAs that run together share a weight tile through L2).  The
+// accumulator is double-buffered in tensor memory (2 x 256 columns): the eight epilogue warps drain
+// tile i while the MMA thread fills tile i + 1, and the TMA ring runs on across tile borders, so the
+// per-tile ramp (barrier set-up, allocation, first-load latency) is paid once per CTA.
+// Warps: 0 = TMA producer, 1 = TMEM owner + MMA issuer, 2..9 = epilogue (lane quarter = warp % 4,
+// column half = (warp - 2) / 4).  Any wait that runs out raises the status word and an abort flag
+// that every other wait polls; the CTA then lets its copies in flight land, frees its tensor
+// memory and returns.
+// ------------------------------------------------------------------------------------------------
+constexpr int P_THREADS = 320;
+constexpr int P_BN = 256;
+
+__device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (int it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+            " selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (it == 0) t0 = global_ns();
+        else if (global_ns() - t0 > 1000000000ull) return false;
+    }
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+template <int STAGES, int EPI>
+__global__ void __launch_bounds__(P_THREADS, 1)
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
+                       void* __restrict__ out, int M, int N, int num_kb, int m_tiles, int n_tiles,
+                       ArgMax* __restrict__ partials, float* __restrict__ logits, int n_parts,
+                       int* __restrict__ status) {
+    constexpr int B_BYTES = P_BN * BK * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t IDESC = instr_desc(BM, P_BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * STAGES + 5];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+    __shared__ int issued_s, consumed_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int total = m_tiles * n_tiles;
+    const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t accf0 = smem_u32(&bars[2 * STAGES]), acce0 = smem_u32(&bars[2 * STAGES + 2]);
+    const uint32_t drain = smem_u32(&bars[2 * STAGES + 4]);
+    const int first = blockIdx.x;
+    const int pre = (first < total) ? (num_kb < STAGES ? num_kb : STAGES) : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accf0, 1); mbar_init(accf0 + 8, 1);
+        mbar_init(acce0, 8); mbar_init(acce0 + 8, 8);
+        mbar_init(drain, 1);
+        abort_s = 0; issued_s = 0; consumed_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // weight tiles of the first stages fly while the kernel that produces x is still running
+        const int n0 = (first / m_tiles) * P_BN;
+        for (int kb = 0; kb < pre; ++kb) {
+            mbar_expect_tx(full0 + 8 * kb, STAGE_BYTES);
+            tma_load_2d(tiles + kb * STAGE_BYTES + A_BYTES, &tma_w, kb * BK, n0, full0 + 8 * kb);
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();
+    const bool dead = status != nullptr && *status != 0;      // an earlier kernel gave up
+    const int my_last = dead ? (pre > 0 ? first + 1 : first) : total;   // a dead CTA only lets its copies land
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = first; tile < my_last && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * P_BN;
+                const int kb_end = dead ? pre : num_kb;
+                for (int kb = 0; kb < kb_end; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t a = tiles + s * STAGE_BYTES;
+                    if (it < pre) {                       // weights already under way: add the rows of x
+                        tma_load_2d(a, &tma_x, kb * BK, m0, full0 + 8 * s);
+                        continue;
+                    }
+                    if (!mbar_wait_or_abort(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, &abort_s)) {
+                        abort_s = 1; if (status) atomicExch(status, 2); ok = false; break;
+                    }
+                    mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_2d(a, &tma_x, kb * BK, m0, full0 + 8 * s);
+                    tma_load_2d(a + A_BYTES, &tma_w, kb * BK, n0, full0 + 8 * s);
+                }
+            }
+            issued_s = it;
+            pdl_trigger();               // every load of this CTA is issued: the successor may start
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, i = 0;
+            bool ok = true;
+            for (int tile = first; tile < my_last && ok; tile += gridDim.x, ++i) {
+                const int buf = i & 1;
+                const uint32_t d_tmem = tmem_base + buf * P_BN;
+                if (!dead && !mbar_wait_or_abort(acce0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_s)) {
+                    abort_s = 1; if (status) atomicExch(status, 5); ok = false; break;
+                }
+                tc_fence_after();
+                const int kb_end = dead ? pre : num_kb;
+                for (int kb = 0; kb < kb_end; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait_or_abort(full0 + 8 * s, (it / STAGES) & 1, &abort_s)) {
+                        abort_s = 1; if (status) atomicExch(status, 3); ok = false; break;
+                    }
+                    if (dead) continue;
+                    tc_fence_after();
+                    const uint32_t a = tiles + s * STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma(d_tmem, smem_desc_sw128(a + k * 32), smem_desc_sw128(a + A_BYTES + k * 32), IDESC,
+                               (kb | k) != 0 ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);           // frees the stage once these MMAs have read it
+                }
+                if (ok && !dead) tc_commit(accf0 + 8 * buf);
+            }
+            consumed_s = it;
+            if (!ok) {                                   // let the MMAs already issued finish before the memory goes
+                tc_commit(drain);
+                mbar_wait(drain, 0);
+            }
+        }
+    } else if (!dead) {
+        // ---- epilogue: thread = output row (TMEM lane), 32-column chunks of this warp's column half ----
+        const int q = warp & 3, ch = (warp - 2) >> 2;
+        int i = 0;
+        for (int tile = first; tile < total; tile += gridDim.x, ++i) {
+            const int buf = i & 1;
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * P_BN + ch * (P_BN / 2);
+            // one outcome for the whole warp: tcgen05.ld below needs all 32 lanes
+            if (!__all_sync(0xffffffffu, mbar_wait_or_abort(accf0 + 8 * buf, (i >> 1) & 1, &abort_s))) {
+                if (lane == 0) { abort_s = 1; if (status) atomicExch(status, 4); }
+                break;
+            }
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll 1
+            for (int c = 0; c < P_BN / 64; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN + ch * (P_BN / 2) + c * 32, r);
+                const int col0 = n0 + c * 32;
+                if (row >= M || col0 >= N) continue;
+                epi_chunk<EPI>(r, out, logits, M, N, row, col0, 0, bv, bi);
+            }
+            // this warp has read its part of the accumulator: hand the buffer back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+            if (EPI == EPI_ARGMAX && row < M && n0 < N) partials[(size_t)row * n_parts + (n0 >> 7)] = ArgMax{bv, bi};
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && abort_s) {
+        // copies issued but never consumed must land before the shared memory is given up
+        for (int k = consumed_s; k < issued_s; ++k) mbar_wait(full0 + 8 * (k % STAGES), (k / STAGES) & 1);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -325,6 +531,54 @@ cudaError_t run_tc(const uint16_t* x, const uint16_t* W, void* out, int M, int N
     return launch_k(kern, grid, dim3(NUM_THREADS), smem, st, mx, mw, out, M, N, K / BK, partials, logits, n_parts, status);
 }
 
+template <int STAGES, int EPI>
+cudaError_t run_tc_persist(const uint16_t* x, const uint16_t* W, void* out, int M, int N, int K, int sms,
+                           ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
+    constexpr size_t smem = (size_t)STAGES * (A_BYTES + P_BN * BK * 2) + 1024;
+    static bool attr_done = false;
+    auto kern = gemm_tc_persist_kernel<STAGES, EPI>;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_done = true;
+    }
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, W, N, K, P_BN)) return cudaErrorInvalidValue;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + P_BN - 1) / P_BN;
+    const int total = m_tiles * n_tiles;
+    return launch_k(kern, dim3(total < sms ? total : sms), dim3(P_THREADS), smem, st, mx, mw, out, M, N, K / BK,
+                    m_tiles, n_tiles, partials, logits, n_parts, status);
+}
+
+int sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
+// the persistent form pays from about one wave of 128 x 256 tiles (Q35_GEMM_PERSIST_MIN overrides)
+bool use_persist(int rows, int N) {
+    static int mode = -1;                                // Q35_GEMM_PERSIST=0 keeps the one-tile-per-CTA form
+    if (mode < 0) {
+        const char* env = std::getenv("Q35_GEMM_PERSIST");
+        mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    if (!mode) return false;
+    const int total = ((rows + BM - 1) / BM) * ((N + P_BN - 1) / P_BN);
+    static int min_tiles = 0;
+    if (min_tiles == 0) {
+        const char* env = std::getenv("Q35_GEMM_PERSIST_MIN");
+        min_tiles = env != nullptr ? std::atoi(env) : 0;
+        if (min_tiles <= 0) min_tiles = 128;             // measured: wins from about one wave of tiles up
+    }
+    return total >= min_tiles;
+}
+
 }  // namespace
 
 bool linear_tc_eligible(int rows, int N, int K) { return rows >= 64 && N >= 128 && K % BK == 0; }
@@ -351,6 +605,12 @@ cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* 
 cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
                              ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
     const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
+    if (use_persist(rows, N)) {
+        const int sms = sm_count();
+        if (epi == EPI_ARGMAX) return run_tc_persist<4, EPI_ARGMAX>(x, W, out, rows, N, K, sms, partials, logits, n_parts, status, st);
+        if (epi == EPI_PLAIN) return run_tc_persist<4, EPI_PLAIN>(x, W, out, rows, N, K, sms, partials, logits, n_parts, status, st);
+        if (epi == EPI_SWIGLU) return run_tc_persist<4, EPI_SWIGLU>(x, W, out, rows, N, K, sms, partials, logits, n_parts, status, st);
+    }
     if (epi == EPI_ARGMAX)
         return run_tc<128, 3, EPI_ARGMAX>(x, W, out, rows, N, K, 1, partials, logits, n_parts, status, st);
     if (epi == EPI_PLAIN) {

@@ -102,7 +102,27 @@ def test_linear_shapes(eng, rows):
     note(f"linear_rows{rows}_worst_rel_l2", worst)
 
 
-@pytest.mark.parametrize("rows", [1, 5, 16, 17, 64, 100, 128, 300])
+@pytest.mark.parametrize("rows", [1999, 4032])
+def test_linear_many_rows(eng, rows):
+    """Bodies of thousands of rows (two or more waves of 128 x 256 tiles: the persistent tensor-core
+    form with the double-buffered accumulator), ragged last row tile and ragged last column tile,
+    vs an f32 matmul of the same bf16 operands on the device."""
+    for name, N, K in [("gdn_in_proj", 8224, 1024), ("attn_in_proj", 5120, 1024), ("down_proj", 1024, 3584)]:
+        g = torch.Generator().manual_seed(N + rows)
+        x = cu(torch.randn((rows, K), generator=g).to(torch.bfloat16))
+        Wt = cu((torch.randn((N, K), generator=g) * 0.02).to(torch.bfloat16))
+        out = eng.op_linear(x, Wt).float()
+        ref = x.float() @ Wt.float().t()
+        err = rel_l2(out.cpu(), ref.to(torch.bfloat16).float().cpu())
+        assert err < 5e-3, (name, rows, err)
+        # every row and every column tile was written: no element left at the fill value
+        worst_row = ((out - ref).norm(dim=1) / ref.norm(dim=1)).max().item()
+        worst_col = ((out - ref).norm(dim=0) / ref.norm(dim=0)).max().item()
+        assert worst_row < 1e-2 and worst_col < 1e-2, (name, rows, worst_row, worst_col)
+        note(f"linear_{name}_rows{rows}", err)
+
+
+@pytest.mark.parametrize("rows", [1, 5, 16, 17, 64, 100, 128, 300, 1999])
 def test_mlp_gateup_and_down(eng, weights, rows):
     pre = O.LM + "layers.0.mlp."
     g = torch.Generator().manual_seed(rows + 5)
