@@ -273,6 +273,17 @@ class Engine:
         self.embed = dev[W.LM + "embed_tokens.weight"]
         del dev
 
+    @classmethod
+    def from_checkpoint(cls, model_dir, max_rows: int, mtp: bool = True, verify: bool = False, vocab: int | None = None):
+        """Engine over a checkpoint directory in the reference's safetensors format
+        (engine/loader.h:118-141): shards resolved, names normalised, vision tensors skipped, the
+        tied head aliased, weights copied to the device once.  Returns (engine, load stats)."""
+        from .checkpoint import WeightStore
+        store, stats = WeightStore.load(model_dir, device="cuda", vocab=vocab, mtp=mtp, verify=verify)
+        if verify and stats.verify_failures:
+            raise Q35Error(1, "checkpoint verification failed: " + "; ".join(stats.verify_failures[:3]))
+        return cls(store.checkpoint_dict(), max_rows=max_rows, mtp=mtp), stats
+
     def small_step_trace(self, n: int = 320):
         """Nanosecond clock of CTA 0 at every barrier of the last profiled few-lane step."""
         buf = (C.c_ulonglong * n)()
