@@ -200,6 +200,21 @@ int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const
  * needs. */
 int q35_mtp_verify(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur, const int* cand,
                    int* emit, int* n_emit, uint16_t* h_next, void* stream);
+/* Depth-k rounds (k = 1 or 2; 2 is the reference's shipped round, engine/mtp_accept.h:87-140).
+ * q35_mtp_state_reserve_depth allocates the k shadow state buffers a depth-k round checkpoints into
+ * (one per body row except the last, engine/mtp_accept.h:135-140) and the chaining scratch.
+ * q35_mtp_draft_k runs k chained drafts (draft j reads the block's output hidden and the proposal of
+ * draft j-1, position pos + j; speccheck/mtp.py:148-153): proposals [lanes][k].
+ * q35_mtp_verify_k feeds [cur, cand_1..cand_k] at positions p..p+k, accepts the LONGEST CORRECT
+ * PREFIX n of the candidates (engine/mtp_accept.h:113-123), emits cand_1..cand_n then the target's
+ * own token after them: emit [lanes][k+1] (unused slots -1), n_emit [lanes] = n + 1, state left
+ * at p + n + 1 (n < k: the lane is pointed at the checkpoint after row n and the round's k draft
+ * rows leave the draft cache, speccheck/mtp.py:163-166), h_next [lanes][1024] = final-norm row n. */
+int q35_mtp_state_reserve_depth(q35_mtp_state* m, int k);
+int q35_mtp_draft_k(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                    const int* pos, int k, int* proposals, void* stream);
+int q35_mtp_verify_k(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur, const int* cands,
+                     int k, int* emit, int* n_emit, uint16_t* h_next, void* stream);
 
 /* ---- single stages (what the per-stage parity tests and the projection/recurrence benchmark
  * slices call; each replaces one reference launcher) ------------------------------------------- */

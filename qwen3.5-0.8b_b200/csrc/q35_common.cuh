@@ -177,18 +177,27 @@ cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* t
                             uint16_t* normed_out, int rows, cudaStream_t st,
                             const float* delta_parts = nullptr, int n_split = 0);
 
+// Speculative verify keeps the state after each non-final row of its body in a shadow buffer, so a
+// rejected candidate is undone by pointing the lane at another buffer: depth k needs k + 1 buffers.
+constexpr int kStateBufs = 3;
+template <typename T>
+__host__ __device__ __forceinline__ T* pick_buf(T* const (&a)[kStateBufs], int i) {
+    return i == 0 ? a[0] : (i == 1 ? a[1] : a[2]);      // selects, not an indexed copy of the parameter block
+}
+
 struct GdnParams {
     const uint16_t* proj;      // [lanes*T][8224]
     const uint16_t* conv_w;    // [6144][4]
     const uint16_t* A_log;     // [16]
     const uint16_t* dt_bias;   // [16]
     const uint16_t* norm_w;    // [128]
-    float* S[2];               // two state buffers [lanes][16][128][128]; S[1] may be null
-    uint16_t* win[2];          // two window buffers [lanes][3][6144]; win[1] may be null
+    float* S[kStateBufs];      // state buffers [lanes][16][128][128]; only S[0] must exist
+    uint16_t* win[kStateBufs]; // window buffers [lanes][3][6144], allocated like S
     const int* sel;            // [lanes] live buffer index per lane, or null (= 0)
     uint16_t* y;               // [lanes*T][2048]
     int lanes, T;
-    int checkpoint;            // 1: T == 2, state after token 0 goes to the non-live buffer
+    int checkpoint;            // c > 0: T == c + 1; the state after token t < c goes to buffer
+                               // (sel + 1 + t) mod (c + 1), the state after the last token stays live
     int* status;               // device word raised to 1 if a bounded wait expires (may be null)
 };
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st);

@@ -97,9 +97,9 @@ struct q35_engine {
 struct q35_state {
     q35_engine* e = nullptr;
     int lanes = 0, max_ctx = 0, pages_per_lane = 0;
-    float* S[2] = {nullptr, nullptr};          // [18][lanes][16][128][128]
-    uint16_t* win[2] = {nullptr, nullptr};     // [18][lanes][3][6144]
-    int* sel = nullptr;                        // [lanes], allocated with the MTP shadow buffers
+    float* S[kStateBufs] = {nullptr, nullptr, nullptr};        // [18][lanes][16][128][128]; [1], [2]: MTP shadows
+    uint16_t* win[kStateBufs] = {nullptr, nullptr, nullptr};   // [18][lanes][3][6144]
+    int* sel = nullptr;                        // [lanes] live buffer per lane, allocated with the MTP shadow buffers
     uint16_t *kpool = nullptr, *vpool = nullptr;
     int* table = nullptr;                      // [lanes][6][pages_per_lane]
     int* pos = nullptr;                        // [lanes]
@@ -119,6 +119,10 @@ struct q35_mtp_state {
     int* table = nullptr;                      // [lanes][pages_per_lane]
     int* n = nullptr;                          // [lanes] rows in the draft cache
     int host_n_hi = 0;
+    int depth = 1;                             // candidates per round the shadow buffers allow
+    uint16_t* h_tmp = nullptr;                 // [lanes][1024] a draft's output hidden, input of the next
+    int* pos_tmp = nullptr;                    // [lanes]
+    int* prop_tmp = nullptr;                   // [lanes]
     long long n_pages = 0;
     alignas(64) unsigned char kmap[kTensorMapBytes];
     alignas(64) unsigned char vmap[kTensorMapBytes];
@@ -142,34 +146,57 @@ static void free_all(std::vector<void*>& owner) {
 // ------------------------------------------------------------------------------------------------
 // small kernels that belong to the bodies
 // ------------------------------------------------------------------------------------------------
-__global__ void interleave2_kernel(const int* __restrict__ a, const int* __restrict__ b,
-                                   int* __restrict__ out, int n) {
+// body ids of a verify round: row (lane, 0) = cur, rows (lane, 1..k) = the lane's candidates
+__global__ void verify_ids_kernel(const int* __restrict__ cur, const int* __restrict__ cand, int k,
+                                  int* __restrict__ out, int lanes) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) { out[2 * i] = a[i]; out[2 * i + 1] = b[i]; }
+    if (i >= lanes * (k + 1)) return;
+    const int lane_id = i / (k + 1), j = i % (k + 1);
+    out[i] = j == 0 ? cur[lane_id] : cand[lane_id * k + j - 1];
+}
+__global__ void add_const_kernel(const int* __restrict__ in, int c, int* __restrict__ out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = in[i] + c;
+}
+__global__ void scatter_col_kernel(const int* __restrict__ in, int* __restrict__ out, int stride, int col, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[(size_t)i * stride + col] = in[i];
 }
 
-// Depth-1 accept rule, all on the device (no host round trip): one warp per lane.
+// Accept rule of a depth-k round, all on the device (no host round trip): one warp per lane.
+// tgt [lanes][k+1]: greedy ids of the body rows; cand [lanes][k].  The round accepts the LONGEST
+// CORRECT PREFIX n of its candidates (engine/mtp_accept.h:113-123), emits cand[0..n) then tgt[n],
+// and for n < k points the lane at the shadow buffer that holds the state after row n.  A round
+// that did not accept everything also drops the k rows its drafts appended to the draft cache
+// (speccheck/mtp.py:163-166).
 __global__ void mtp_verdict_kernel(const int* __restrict__ cand, const int* __restrict__ tgt,
-                                   const uint16_t* __restrict__ normed2, int* __restrict__ emit,
+                                   const uint16_t* __restrict__ normed, int k, int* __restrict__ emit,
                                    int* __restrict__ n_emit, uint16_t* __restrict__ h_next,
                                    int* __restrict__ pos, int* __restrict__ sel,
                                    int* __restrict__ mtp_n, int lanes) {
     const int lane_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int ln = threadIdx.x & 31;
     if (lane_id >= lanes) return;
-    const int t0 = tgt[2 * lane_id], t1 = tgt[2 * lane_id + 1];
-    const bool ok = cand[lane_id] == t0;
+    const int* c = cand + (size_t)lane_id * k;
+    const int* t = tgt + (size_t)lane_id * (k + 1);
+    int n = 0;
+    while (n < k && c[n] == t[n]) ++n;
     if (ln == 0) {
-        emit[2 * lane_id] = ok ? cand[lane_id] : t0;
-        emit[2 * lane_id + 1] = ok ? t1 : -1;
-        n_emit[lane_id] = ok ? 2 : 1;
-        pos[lane_id] += ok ? 2 : 1;
-        if (!ok) { sel[lane_id] ^= 1; mtp_n[lane_id] -= 1; }
+        int* em = emit + (size_t)lane_id * (k + 1);
+        for (int i = 0; i <= k; ++i) em[i] = i < n ? c[i] : (i == n ? t[n] : -1);
+        n_emit[lane_id] = n + 1;
+        pos[lane_id] += n + 1;
+        if (n < k) {
+            int b = sel[lane_id] + 1 + n;
+            if (b > k) b -= k + 1;
+            sel[lane_id] = b;
+            mtp_n[lane_id] -= k;
+        }
     }
-    const uint4* src = reinterpret_cast<const uint4*>(normed2 + (size_t)(2 * lane_id + (ok ? 1 : 0)) * kHidden);
+    const uint4* src = reinterpret_cast<const uint4*>(normed + ((size_t)lane_id * (k + 1) + n) * kHidden);
     uint4* dst = reinterpret_cast<uint4*>(h_next + (size_t)lane_id * kHidden);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) dst[c * 32 + ln] = src[c * 32 + ln];
+    for (int q = 0; q < 4; ++q) dst[q * 32 + ln] = src[q * 32 + ln];
 }
 
 // embedding gather for bodies whose ids are a [lanes][T_total] matrix and the body takes columns
@@ -450,7 +477,7 @@ extern "C" int q35_state_reset(q35_state* s, void* stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const size_t sn = (size_t)kGdnLayers * s->lanes * kGdnHeads * kDk * kDv;
     const size_t wn = (size_t)kGdnLayers * s->lanes * 3 * kConvCh;
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kStateBufs; ++b) {
         if (s->S[b]) CK(cudaMemsetAsync(s->S[b], 0, sn * sizeof(float), st));
         if (s->win[b]) CK(cudaMemsetAsync(s->win[b], 0, wn * sizeof(uint16_t), st));
     }
@@ -535,7 +562,7 @@ static int host_sel(q35_state* s, int lane, cudaStream_t st, int* out) {
     if (s->sel) {
         CK(cudaMemcpyAsync(out, s->sel + lane, sizeof(int), cudaMemcpyDeviceToHost, st));
         CK(cudaStreamSynchronize(st));
-        *out &= 1;
+        if (*out < 0 || *out >= kStateBufs || s->S[*out] == nullptr) return fail(Q35_ERR_STATE, "lane %d selects a state buffer that does not exist", lane);
     }
     return Q35_OK;
 }
@@ -632,7 +659,7 @@ static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int chec
             gp.norm_w = L.gdn_norm;
             const size_t so = (size_t)gslot * s->lanes * kGdnHeads * kDk * kDv;
             const size_t wo = (size_t)gslot * s->lanes * 3 * kConvCh;
-            for (int b = 0; b < 2; ++b) {
+            for (int b = 0; b < kStateBufs; ++b) {
                 gp.S[b] = s->S[b] ? s->S[b] + so : nullptr;
                 gp.win[b] = s->win[b] ? s->win[b] + wo : nullptr;
             }
@@ -810,12 +837,10 @@ extern "C" int q35_mtp_state_destroy(q35_mtp_state* m) {
     return Q35_OK;
 }
 
-extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
-                             const int* pos, int* proposal, void* stream) {
-    REQUIRE(e && m && h_norm && y_next && pos && proposal, Q35_ERR_ARG, "q35_mtp_draft: null argument");
-    REQUIRE(m->e == e, Q35_ERR_STATE, "q35_mtp_draft: state belongs to another engine");
-    REQUIRE(m->host_n_hi + 1 <= m->max_ctx, Q35_ERR_CAPACITY, "draft cache full (%d rows)", m->max_ctx);
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+// One draft pass of the MTP block for every lane (speccheck/mtp.py:57-83): proposal ids, the
+// block's output hidden in e->normed, one row appended to the draft cache.
+static int draft_once(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                      const int* pos, int* proposal, cudaStream_t st) {
     const int rows = m->lanes;
     const PackedLayer& L = e->mtp_layer;
     // pair = [ N(E[y]; norm_emb) | N(h; norm_hid) ], written as two 1024-wide halves of [rows][2048]
@@ -848,23 +873,102 @@ extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_
     return Q35_OK;
 }
 
+extern "C" int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                             const int* pos, int* proposal, void* stream) {
+    REQUIRE(e && m && h_norm && y_next && pos && proposal, Q35_ERR_ARG, "q35_mtp_draft: null argument");
+    REQUIRE(m->e == e, Q35_ERR_STATE, "q35_mtp_draft: state belongs to another engine");
+    REQUIRE(m->host_n_hi + 1 <= m->max_ctx, Q35_ERR_CAPACITY, "draft cache full (%d rows)", m->max_ctx);
+    pdl_set_rows(m->lanes);
+    return draft_once(e, m, h_norm, y_next, pos, proposal, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int q35_mtp_state_reserve_depth(q35_mtp_state* m, int k) {
+    REQUIRE(m && m->s, Q35_ERR_ARG, "q35_mtp_state_reserve_depth: null state");
+    REQUIRE(k >= 1 && k < kStateBufs, Q35_ERR_ARG, "q35_mtp_state_reserve_depth: depth %d, supported 1..%d", k, kStateBufs - 1);
+    q35_state* s = m->s;
+    REQUIRE((k + 1) * s->lanes <= m->e->head_rows_cap && (k + 1) * s->lanes <= m->e->max_rows, Q35_ERR_CAPACITY,
+            "a depth-%d round needs %d rows, the engine holds %d", k, (k + 1) * s->lanes,
+            m->e->head_rows_cap < m->e->max_rows ? m->e->head_rows_cap : m->e->max_rows);
+    const size_t sn = (size_t)kGdnLayers * s->lanes * kGdnHeads * kDk * kDv;
+    const size_t wn = (size_t)kGdnLayers * s->lanes * 3 * kConvCh;
+    cudaError_t ce = cudaSuccess;
+    for (int b = 1; b <= k && ce == cudaSuccess; ++b) {
+        if (s->S[b]) continue;
+        ce = dev_alloc(s->allocs, &s->S[b], sn);
+        if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->win[b], wn);
+        if (ce == cudaSuccess) ce = cudaMemset(s->S[b], 0, sn * sizeof(float));
+        if (ce == cudaSuccess) ce = cudaMemset(s->win[b], 0, wn * sizeof(uint16_t));
+    }
+    if (ce == cudaSuccess && !m->h_tmp) {
+        ce = dev_alloc(m->allocs, &m->h_tmp, (size_t)m->lanes * kHidden);
+        if (ce == cudaSuccess) ce = dev_alloc(m->allocs, &m->pos_tmp, (size_t)m->lanes);
+        if (ce == cudaSuccess) ce = dev_alloc(m->allocs, &m->prop_tmp, (size_t)m->lanes);
+    }
+    if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+    if (ce != cudaSuccess) return fail(Q35_ERR_CUDA, "q35_mtp_state_reserve_depth: %s", cudaGetErrorString(ce));
+    if (k > m->depth) m->depth = k;
+    return Q35_OK;
+}
+
+// k chained drafts (speccheck/mtp.py:148-153): draft j reads the hidden the block produced for
+// draft j - 1 and the token draft j - 1 proposed, at position pos + j.
+extern "C" int q35_mtp_draft_k(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                               const int* pos, int k, int* proposals, void* stream) {
+    REQUIRE(e && m && h_norm && y_next && pos && proposals, Q35_ERR_ARG, "q35_mtp_draft_k: null argument");
+    REQUIRE(m->e == e, Q35_ERR_STATE, "q35_mtp_draft_k: state belongs to another engine");
+    REQUIRE(k >= 1 && k <= m->depth && m->h_tmp, Q35_ERR_STATE, "q35_mtp_draft_k: depth %d not reserved (q35_mtp_state_reserve_depth)", k);
+    REQUIRE(m->host_n_hi + k <= m->max_ctx, Q35_ERR_CAPACITY, "draft cache full (%d rows)", m->max_ctx);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int L = m->lanes;
+    pdl_set_rows(L);
+    const uint16_t* h = h_norm;
+    const int* y = y_next;
+    const int* p = pos;
+    for (int j = 0; j < k; ++j) {
+        int rc = draft_once(e, m, h, y, p, m->prop_tmp, st);
+        if (rc != Q35_OK) return rc;
+        scatter_col_kernel<<<(L + 255) / 256, 256, 0, st>>>(m->prop_tmp, proposals, k, j, L);
+        CK(cudaGetLastError());
+        if (j + 1 < k) {
+            CK(copy_rows(m->h_tmp, e->normed, (size_t)L * kHidden, st));
+            add_const_kernel<<<(L + 255) / 256, 256, 0, st>>>(pos, j + 1, m->pos_tmp, L);
+            CK(cudaGetLastError());
+            // prop_tmp is read by the next pass's first kernel and rewritten by its last: stream order suffices
+            h = m->h_tmp; y = m->prop_tmp; p = m->pos_tmp;
+        }
+    }
+    return Q35_OK;
+}
+
+static int verify_round(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur, const int* cand, int k,
+                        int* emit, int* n_emit, uint16_t* h_next, cudaStream_t st) {
+    const int L = s->lanes;
+    verify_ids_kernel<<<(L * (k + 1) + 255) / 256, 256, 0, st>>>(cur, cand, k, e->tok2, L);
+    CK(cudaGetLastError());
+    int rc = run_body(e, s, e->tok2, k + 1, k, st);
+    if (rc != Q35_OK) return rc;
+    rc = run_head(e, e->normed, (k + 1) * L, e->tgt, nullptr, st);
+    if (rc != Q35_OK) return rc;
+    mtp_verdict_kernel<<<(L + 7) / 8, 256, 0, st>>>(cand, e->tgt, e->normed, k, emit, n_emit, h_next,
+                                                    s->pos, s->sel, m->n, L);
+    CK(cudaGetLastError());
+    s->host_pos_hi += k + 1;   // upper bound: lanes that rejected sit lower
+    return Q35_OK;
+}
+
 extern "C" int q35_mtp_verify(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur,
                               const int* cand, int* emit, int* n_emit, uint16_t* h_next, void* stream) {
     REQUIRE(e && s && m && cur && cand && emit && n_emit && h_next, Q35_ERR_ARG, "q35_mtp_verify: null argument");
     REQUIRE(m->s == s && s->e == e && s->S[1] && s->sel, Q35_ERR_STATE, "q35_mtp_verify: MTP state not attached to this state");
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int L = s->lanes;
-    interleave2_kernel<<<(L + 255) / 256, 256, 0, st>>>(cur, cand, e->tok2, L);
-    CK(cudaGetLastError());
-    int rc = run_body(e, s, e->tok2, 2, 1, st);
-    if (rc != Q35_OK) return rc;
-    rc = run_head(e, e->normed, 2 * L, e->tgt, nullptr, st);
-    if (rc != Q35_OK) return rc;
-    mtp_verdict_kernel<<<(L + 7) / 8, 256, 0, st>>>(cand, e->tgt, e->normed, emit, n_emit, h_next,
-                                                    s->pos, s->sel, m->n, L);
-    CK(cudaGetLastError());
-    s->host_pos_hi += 2;   // upper bound: lanes that rejected sit one lower
-    return Q35_OK;
+    return verify_round(e, s, m, cur, cand, 1, emit, n_emit, h_next, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int q35_mtp_verify_k(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur,
+                                const int* cands, int k, int* emit, int* n_emit, uint16_t* h_next, void* stream) {
+    REQUIRE(e && s && m && cur && cands && emit && n_emit && h_next, Q35_ERR_ARG, "q35_mtp_verify_k: null argument");
+    REQUIRE(m->s == s && s->e == e && s->sel, Q35_ERR_STATE, "q35_mtp_verify_k: MTP state not attached to this state");
+    REQUIRE(k >= 1 && k <= m->depth && s->S[k], Q35_ERR_STATE, "q35_mtp_verify_k: depth %d not reserved (q35_mtp_state_reserve_depth)", k);
+    return verify_round(e, s, m, cur, cands, k, emit, n_emit, h_next, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -927,7 +1031,7 @@ extern "C" int q35_op_gdn_step(uint16_t* proj, const uint16_t* conv_w, const uin
             "q35_op_gdn_step: S / conv_w / proj / window must be 16-byte aligned");
     GdnParams gp{};
     gp.proj = proj; gp.conv_w = conv_w; gp.A_log = A_log; gp.dt_bias = dt_bias; gp.norm_w = norm_w;
-    gp.S[0] = S; gp.S[1] = nullptr; gp.win[0] = window; gp.win[1] = nullptr; gp.sel = nullptr;
+    gp.S[0] = S; gp.win[0] = window; gp.sel = nullptr;      // GdnParams gp{} left the shadow buffers null
     gp.y = y; gp.lanes = lanes; gp.T = T; gp.checkpoint = 0;
     if (T >= kGdnChunkMinT)
         CK(launch_gdn_chunked(gp, static_cast<cudaStream_t>(stream)));

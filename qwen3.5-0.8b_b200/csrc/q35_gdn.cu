@@ -63,9 +63,9 @@ constexpr size_t kGdnSmemBytes = kTileBytes + kInBytes;
 // rows of this step's projection; the first may be issued before the projection kernel has ended.
 __device__ __forceinline__ void item_fetch_state(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
                                                  uint32_t in_addr, uint32_t bar) {
-    const int sel = p.sel != nullptr ? (p.sel[lane_id] & 1) : 0;
-    const float* S = (sel ? p.S[1] : p.S[0]) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
-    const uint16_t* win = (sel ? p.win[1] : p.win[0]) + (size_t)lane_id * 3 * kConvCh;
+    const int sel = p.sel != nullptr ? p.sel[lane_id] : 0;
+    const float* S = pick_buf(p.S, sel) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
+    const uint16_t* win = pick_buf(p.win, sel) + (size_t)lane_id * 3 * kConvCh;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
     bulk_g2s(tile_addr, S, kTileBytes, bar);
@@ -147,11 +147,11 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 
     uint32_t phase = 0;
     for (int lane_id = blockIdx.x / kGdnHeads; lane_id < p.lanes; lane_id += lane_stride) {
-        const int sel = p.sel != nullptr ? (p.sel[lane_id] & 1) : 0;
+        const int sel = p.sel != nullptr ? p.sel[lane_id] : 0;
         const size_t s_off = ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
         const size_t w_off = (size_t)lane_id * 3 * kConvCh;
-        float* S_live = (sel ? p.S[1] : p.S[0]) + s_off;
-        uint16_t* win_live = (sel ? p.win[1] : p.win[0]) + w_off;
+        float* S_live = pick_buf(p.S, sel) + s_off;
+        uint16_t* win_live = pick_buf(p.win, sel) + w_off;
 
         // ---- prefetched tile and inputs: shared memory -> registers ------------------------------
         if (!mbar_wait_bounded(bar, phase)) {
@@ -289,13 +289,15 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
                     make_uint2(pack_bf2(out[0], out[1]), pack_bf2(out[2], out[3]));
             }
 
-            // ---- checkpoint after the first of two tokens (speculative verify) -----------------
-            if (p.checkpoint && t == 0) {
-                float4* Sc = reinterpret_cast<float4*>((sel ? p.S[0] : p.S[1]) + s_off);
+            // ---- checkpoint after every non-final token of a speculative verify body -------------
+            if (t < p.checkpoint) {
+                int cb = sel + 1 + t;
+                if (cb > p.checkpoint) cb -= p.checkpoint + 1;
+                float4* Sc = reinterpret_cast<float4*>(pick_buf(p.S, cb) + s_off);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) Sc[(warp * 16 + r) * 32 + ln] = s[r];
                 if (tid < 128) {
-                    uint16_t* wc = (sel ? p.win[0] : p.win[1]) + w_off;
+                    uint16_t* wc = pick_buf(p.win, cb) + w_off;
 #pragma unroll
                     for (int kind = 0; kind < 3; ++kind)
 #pragma unroll
@@ -320,7 +322,12 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
     if (p.lanes <= 0 || p.T <= 0 || p.lanes > 65535) return cudaErrorInvalidValue;
-    if (p.checkpoint && (p.T != 2 || p.S[1] == nullptr || p.win[1] == nullptr)) return cudaErrorInvalidValue;
+    if (p.checkpoint < 0 || p.checkpoint >= kStateBufs) return cudaErrorInvalidValue;
+    if (p.checkpoint > 0) {
+        if (p.T != p.checkpoint + 1) return cudaErrorInvalidValue;
+        for (int b = 0; b <= p.checkpoint; ++b)
+            if (p.S[b] == nullptr || p.win[b] == nullptr) return cudaErrorInvalidValue;
+    }
     static int max_ctas = 0;
     if (max_ctas == 0) {
         int dev = 0, sms = 0;

@@ -31,11 +31,12 @@ constexpr size_t kChunkSmem = (size_t)128 * 128 * 4 + (size_t)C * X_LD * 4 + 2 *
 // grid (lanes, 12), 256 threads, 2 adjacent channels per thread.
 __global__ void __launch_bounds__(256)
 gdn_conv_prep_kernel(uint16_t* __restrict__ proj, const uint16_t* __restrict__ conv_w,
-                     uint16_t* __restrict__ win0, uint16_t* __restrict__ win1, const int* __restrict__ sel,
-                     int T) {
+                     uint16_t* __restrict__ win0, uint16_t* __restrict__ win1, uint16_t* __restrict__ win2,
+                     const int* __restrict__ sel, int T) {
     const int lane_id = blockIdx.x;
     const int c = (blockIdx.y * 256 + threadIdx.x) * 2;
-    uint16_t* win = ((sel != nullptr && (sel[lane_id] & 1)) ? win1 : win0) + (size_t)lane_id * 3 * kConvCh;
+    const int live = sel != nullptr ? sel[lane_id] : 0;
+    uint16_t* win = (live == 0 ? win0 : (live == 1 ? win1 : win2)) + (size_t)lane_id * 3 * kConvCh;
     float tap[2][4], w[2][3];
     {
         const uint4 tw = *reinterpret_cast<const uint4*>(conv_w + (size_t)c * 4);
@@ -77,8 +78,8 @@ __device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__ A_log,
                  const uint16_t* __restrict__ dt_bias, const uint16_t* __restrict__ norm_w,
-                 float* __restrict__ S0, float* __restrict__ S1, const int* __restrict__ sel,
-                 uint16_t* __restrict__ y, int T) {
+                 float* __restrict__ S0, float* __restrict__ S1, float* __restrict__ S2,
+                 const int* __restrict__ sel, uint16_t* __restrict__ y, int T) {
     extern __shared__ __align__(16) unsigned char smem_chunk[];
     float* S_s = reinterpret_cast<float*>(smem_chunk);                 // [128][128]  S[dk][dv]
     float* X_s = S_s + 128 * 128;                                      // [64][256]   [nv | kc]
@@ -98,7 +99,8 @@ gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__
 
     const int h = blockIdx.x, lane_id = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
-    float* S_g = ((sel != nullptr && (sel[lane_id] & 1)) ? S1 : S0) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
+    const int live = sel != nullptr ? sel[lane_id] : 0;
+    float* S_g = (live == 0 ? S0 : (live == 1 ? S1 : S2)) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
     const float negA = -expf(bf2f(A_log[h]));
     const float dtb = bf2f(dt_bias[h]);
     const float q_scale = 0.08838834764831845f;
@@ -406,11 +408,11 @@ cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
         attr_done = true;
     }
     gdn_conv_prep_kernel<<<dim3(p.lanes, kConvCh / 512), 256, 0, st>>>(const_cast<uint16_t*>(p.proj), p.conv_w, p.win[0],
-                                                                  p.win[1], p.sel, p.T);
+                                                                  p.win[1], p.win[2], p.sel, p.T);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     gdn_chunk_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w, p.S[0],
-                                                                       p.S[1], p.sel, p.y, p.T);
+                                                                       p.S[1], p.S[2], p.sel, p.y, p.T);
     return cudaGetLastError();
 }
 

@@ -63,7 +63,8 @@ EXPORTS = [
     "q35_state_sizes_of", "q35_state_create", "q35_state_destroy", "q35_state_reset",
     "q35_state_positions", "q35_state_note_advance", "q35_state_export_lane", "q35_state_import_lane",
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
-    "q35_mtp_state_reset", "q35_mtp_draft", "q35_mtp_verify", "q35_op_add_norm", "q35_op_linear",
+    "q35_mtp_state_reset", "q35_mtp_draft", "q35_mtp_verify", "q35_mtp_state_reserve_depth",
+    "q35_mtp_draft_k", "q35_mtp_verify_k", "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
     "q35_lm_head_argmax_static",
 ]
@@ -190,10 +191,12 @@ class LaneState:
 
 
 class MtpState:
-    def __init__(self, engine: "Engine", state: LaneState, max_ctx: int):
-        self.engine, self.state = engine, state
+    def __init__(self, engine: "Engine", state: LaneState, max_ctx: int, depth: int = 1):
+        self.engine, self.state, self.depth = engine, state, depth
         self.handle = C.c_void_p()
         _check(engine.lib.q35_mtp_state_create(engine.handle, state.handle, max_ctx, C.byref(self.handle)))
+        if depth > 1:
+            _check(engine.lib.q35_mtp_state_reserve_depth(self.handle, depth))
 
     def reset(self):
         _check(self.engine.lib.q35_mtp_state_reset(self.handle, _stream()))
@@ -324,10 +327,10 @@ class Engine:
     def allocate_state(self, lanes: int, max_ctx: int) -> LaneState:
         return LaneState(self, lanes, max_ctx)
 
-    def mtp_allocate(self, state: LaneState, max_ctx: int) -> MtpState:
-        return MtpState(self, state, max_ctx)
+    def mtp_allocate(self, state: LaneState, max_ctx: int, depth: int = 1) -> MtpState:
+        """Draft cache + the shadow state buffers of depth-`depth` rounds (1 or 2 candidates per round)."""
+        return MtpState(self, state, max_ctx, depth)
 
-    # ---- bodies --------------------------------------------------------------------------------
     def decode_step(self, state: LaneState, in_tok: torch.Tensor, out_tok: torch.Tensor | None = None,
                     logits: torch.Tensor | None = None, normed: torch.Tensor | None = None):
         """One greedy step for every lane; tokens are int32 device tensors [lanes]."""
@@ -364,6 +367,25 @@ class Engine:
         return emit, n_emit, h_next
 
     # ---- host-buffer step (what a caller of the reference's decode_step does) ------------------
+    def mtp_draft_k(self, m: MtpState, h_norm, y_next, pos, k: int, proposals=None):
+        """k chained drafts per lane: proposals int32 [lanes, k]."""
+        L = m.state.lanes
+        if proposals is None:
+            proposals = torch.empty((L, k), dtype=torch.int32, device="cuda")
+        _check(self.lib.q35_mtp_draft_k(self.handle, m.handle, _ptr(h_norm), _ptr(y_next), _ptr(pos), k,
+                                        _ptr(proposals), _stream()))
+        return proposals
+
+    def mtp_verify_k(self, state: LaneState, m: MtpState, cur, cands, emit=None, n_emit=None, h_next=None):
+        """Depth-k verify: cands int32 [lanes, k] -> (emit [lanes, k+1], n_emit [lanes], h_next [lanes, 1024])."""
+        L, k = state.lanes, cands.shape[1]
+        emit = torch.empty((L, k + 1), dtype=torch.int32, device="cuda") if emit is None else emit
+        n_emit = torch.empty(L, dtype=torch.int32, device="cuda") if n_emit is None else n_emit
+        h_next = torch.empty((L, 1024), dtype=torch.bfloat16, device="cuda") if h_next is None else h_next
+        _check(self.lib.q35_mtp_verify_k(self.handle, state.handle, m.handle, _ptr(cur), _ptr(cands), k,
+                                         _ptr(emit), _ptr(n_emit), _ptr(h_next), _stream()))
+        return emit, n_emit, h_next
+
     def decode_step_host(self, state: LaneState, tok_host: torch.Tensor, out_host: torch.Tensor,
                          graph: "StepGraph | None" = None):
         """tokens in pinned host memory -> H2D, one step, D2H, synchronise.  Validates ids on the

@@ -153,3 +153,127 @@ def test_verify_needs_mtp_state(eng, pkg, golden):
         eng.mtp_verify(st, m, z, z)
     assert ei.value.code == 4
     m.close(); st.close(); other.close()
+
+
+# ------------------------------------------------------------------------------------ depth 2
+def test_chained_drafts_match_the_oracle(eng, weights, golden):
+    """Two chained drafts on the reference's own (h, y_next, pos): the first proposal is the
+    fixture's, the second the oracle's wherever its f32 top-2 margin exceeds 1e-2."""
+    g = golden["mtp"]
+    st = eng.allocate_state(1, 64)
+    m = eng.mtp_allocate(st, 64, depth=2)
+    h = bf(g["draft_h"])
+    y, pos = int(g["draft_y"][0]), int(g["draft_pos"][0])
+    props = eng.mtp_draft_k(m, h.cuda(), torch.tensor([y], dtype=torch.int32).cuda(),
+                            torch.tensor([pos], dtype=torch.int32).cuda(), 2).cpu()
+    om = O.MtpLane(weights, kv_bf16=True)
+    d1, x1 = om.draft(y, h, pos)
+    dbg = {}
+    d2, _ = om.draft(d1, x1, pos + 1, dbg)
+    assert int(props[0, 0]) == d1 == int(g["draft_id"][0])
+    best, margin = O.top2_margin(dbg["logits"][-1].float())
+    if margin > 1e-2:
+        assert int(props[0, 1]) == d2 == best
+    # a single draft on a fresh cache proposes the same first token
+    m1 = eng.mtp_allocate(st, 64)
+    p1 = eng.mtp_draft(m1, h.cuda(), torch.tensor([y], dtype=torch.int32).cuda(), torch.tensor([pos], dtype=torch.int32).cuda())
+    assert int(p1[0]) == int(props[0, 0])
+    m.close(); m1.close(); st.close()
+
+
+def test_depth2_rounds_equal_plain_greedy(eng, golden):
+    lanes, rounds = 3, 6
+    ids = prompts(golden, lanes)
+    sp = eng.allocate_state(lanes, 64)
+    mp = eng.mtp_allocate(sp, 64, depth=2)
+    y0, _ = eng.prefill(sp, ids)
+    plain = [y0.clone()]
+    for _ in range(3 * rounds):
+        plain.append(eng.decode_step(sp, plain[-1]).clone())
+    plain = torch.stack(plain).cpu()
+
+    ss = eng.allocate_state(lanes, 64)
+    m = eng.mtp_allocate(ss, 64, depth=2)
+    t, h = eng.prefill(ss, ids, want_normed=True)
+    emitted = [[int(x)] for x in t.tolist()]
+    for _ in range(rounds):
+        d = eng.mtp_draft_k(m, h, t, (ss.positions + 1).int(), 2)
+        emit, n_emit, h = eng.mtp_verify_k(ss, m, t, d)
+        em, ne = emit.cpu(), n_emit.cpu()
+        for i in range(lanes):
+            emitted[i].extend(em[i, :int(ne[i])].tolist())
+        t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
+    for i in range(lanes):
+        assert emitted[i] == plain[:len(emitted[i]), i].tolist(), f"lane {i}"
+    assert ss.positions.tolist() == [16 + len(e) - 1 for e in emitted]
+    m.close(); mp.close(); ss.close(); sp.close()
+
+
+def test_depth2_longest_prefix_and_rollback(eng, golden):
+    """Forced candidates: lane 0 rejects both (n = 0), lane 1 accepts one (n = 1), lane 2 accepts
+    both (n = 2); then a second round with the pattern rotated, so every lane's live buffer index
+    moves twice.  After each round a lane's state is bit-identical to the plain run that consumed
+    the same tokens."""
+    lanes = 3
+    ids = prompts(golden, lanes)
+    sp = eng.allocate_state(lanes, 64)
+    mp = eng.mtp_allocate(sp, 64, depth=2)
+    y0, _ = eng.prefill(sp, ids)
+    seq, snaps = [y0.clone()], []
+    for _ in range(8):
+        seq.append(eng.decode_step(sp, seq[-1]).clone())
+        snaps.append([sp.export_lane(i, 64) for i in range(lanes)])      # snaps[j]: after consuming seq[0..j]
+    S = torch.stack(seq).cpu()                                            # S[j, lane]
+
+    ss = eng.allocate_state(lanes, 64)
+    m = eng.mtp_allocate(ss, 64, depth=2)
+    t, h = eng.prefill(ss, ids, want_normed=True)
+    assert torch.equal(t, y0)
+    consumed = [0, 0, 0]                      # tokens of seq consumed per lane
+    for accept in ([0, 1, 2], [2, 0, 1]):
+        cands = torch.empty((lanes, 2), dtype=torch.int32)
+        for i in range(lanes):
+            c = consumed[i]
+            true1, true2 = int(S[c + 1, i]), int(S[c + 2, i])
+            wrong = lambda x: (x + 1) % 248320
+            cands[i, 0] = true1 if accept[i] >= 1 else wrong(true1)
+            cands[i, 1] = true2 if accept[i] >= 2 else wrong(true2)
+        eng.mtp_draft_k(m, h, t, (ss.positions + 1).int(), 2)             # fills the draft cache like a real round
+        emit, n_emit, h = eng.mtp_verify_k(ss, m, t, cands.cuda())
+        assert n_emit.tolist() == [a + 1 for a in accept]
+        for i in range(lanes):
+            c, a = consumed[i], accept[i]
+            want = [int(S[c + 1 + j, i]) for j in range(a + 1)] + [-1] * (2 - a)
+            assert emit[i].tolist() == want, (i, emit[i].tolist(), want)
+            consumed[i] = c + a + 1
+            got, ref = ss.export_lane(i, 64), snaps[consumed[i] - 1][i]
+            assert got["prefix_len"] == ref["prefix_len"] == 16 + consumed[i]
+            assert torch.equal(got["gdn_state"], ref["gdn_state"]), f"lane {i} accept {a}"
+            assert torch.equal(got["conv_window"], ref["conv_window"])
+            n = got["prefix_len"]
+            assert torch.equal(got["kv_keys"][:, :, :n], ref["kv_keys"][:, :, :n])
+            assert torch.equal(got["kv_values"][:, :, :n], ref["kv_values"][:, :, :n])
+        t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
+    # a depth-1 round still works on the three-buffer state, whatever buffer is live
+    d1 = eng.mtp_draft(m, h, t, (ss.positions + 1).int())
+    emit, n_emit, h = eng.mtp_verify(ss, m, t, torch.stack([S[consumed[i] + 1, i] for i in range(lanes)]).int().cuda())
+    assert n_emit.tolist() == [2, 2, 2]
+    for i in range(lanes):
+        got, ref = ss.export_lane(i, 64), snaps[consumed[i] + 1][i]
+        assert torch.equal(got["gdn_state"], ref["gdn_state"])
+    m.close(); mp.close(); ss.close(); sp.close()
+
+
+def test_depth_must_be_reserved(eng, pkg, golden):
+    st = eng.allocate_state(1, 32)
+    m = eng.mtp_allocate(st, 32)                  # depth 1 only
+    z = torch.zeros(1, dtype=torch.int32, device="cuda")
+    z2 = torch.zeros((1, 2), dtype=torch.int32, device="cuda")
+    with pytest.raises(pkg.Q35Error) as ei:
+        eng.mtp_verify_k(st, m, z, z2)
+    assert ei.value.code == 4
+    with pytest.raises(pkg.Q35Error):
+        eng.mtp_draft_k(m, torch.zeros((1, 1024), dtype=torch.bfloat16, device="cuda"), z, z, 2)
+    with pytest.raises(pkg.Q35Error):
+        eng.mtp_allocate(st, 32, depth=3)
+    m.close(); st.close()
