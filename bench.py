@@ -173,12 +173,12 @@ def measure(pkg, eng, lanes: int, prompt: int, steps: int, warmup: int, dist, sa
                 ctx_mid=ctx_mid, prefill_s=prefill_s, clocks=clocks, last_tokens=cur.clone())
 
 
-def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warmup: int = 3) -> dict:
-    """Chunk-64 prefill of `lanes` x `prompt` ids, then `rounds` speculative rounds (MTP draft depth 1,
-    2-token verify), tokens chained on the device.  On random-init weights the draft almost never
-    matches the target, so accepted tok/s is about one token per lane per round."""
-    st = eng.allocate_state(lanes, prompt + 2 * (rounds + warmup) + 8)
-    m = eng.mtp_allocate(st, rounds + warmup + 8)
+def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warmup: int = 3, depth: int = 1) -> dict:
+    """Chunk-64 prefill of `lanes` x `prompt` ids, then `rounds` speculative rounds (`depth` chained MTP
+    drafts, verify of depth + 1 tokens), tokens chained on the device.  On random-init weights the
+    draft almost never matches the target, so accepted tok/s is about one token per lane per round."""
+    st = eng.allocate_state(lanes, prompt + (depth + 1) * (rounds + warmup) + 8)
+    m = eng.mtp_allocate(st, depth * (rounds + warmup) + 8, depth=depth)
     gen = torch.Generator().manual_seed(4000)
     ids = torch.randint(0, eng.vocab, (lanes, prompt), generator=gen, dtype=torch.int32).cuda()
     torch.cuda.synchronize()
@@ -190,9 +190,14 @@ def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warm
 
     def one_round():
         nonlocal t, h
-        d = eng.mtp_draft(m, h, t, (st.positions + 1).int())
-        emit, n_emit, h = eng.mtp_verify(st, m, t, d)
-        t = torch.where(n_emit == 2, emit[:, 1], emit[:, 0]).int().contiguous()
+        pos = (st.positions + 1).int()
+        if depth == 1:
+            d = eng.mtp_draft(m, h, t, pos)
+            emit, n_emit, h = eng.mtp_verify(st, m, t, d)
+        else:
+            d = eng.mtp_draft_k(m, h, t, pos, depth)
+            emit, n_emit, h = eng.mtp_verify_k(st, m, t, d)
+        t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
         return n_emit
 
     for _ in range(warmup):
@@ -208,8 +213,9 @@ def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warm
     n = int(emitted.item())
     m.close()
     st.close()
-    return {"workload": f"configs[4]: {lanes} lanes x {prompt}-token chunk-64 prefill, {rounds} rounds of MTP draft (depth 1) + 2-token verify",
-            "accepted_tok_per_s": round(n / (ms * 1e-3), 1), "accept_rate": round((n - rounds * lanes) / (rounds * lanes), 4),
+    return {"workload": f"configs[4]: {lanes} lanes x {prompt}-token chunk-64 prefill, {rounds} rounds of {depth} chained MTP "
+                        f"draft(s) + {depth + 1}-token verify",
+            "accepted_tok_per_s": round(n / (ms * 1e-3), 1), "accept_rate": round((n - rounds * lanes) / (rounds * lanes * depth), 4),
             "ms_per_round": round(ms / rounds, 4), "prefill_tok_per_s": round(lanes * prompt / prefill_s, 1)}
 
 
@@ -361,6 +367,7 @@ def main():
     mtp = None
     if rank == 0 and not args.no_mtp and eng.has_mtp:
         mtp = measure_mtp(eng)
+        mtp["depth2"] = measure_mtp(eng, depth=2)      # the reference's default round width
     if dist:
         import torch.distributed as td
         td.barrier()
