@@ -165,6 +165,12 @@ def measure(pkg, eng, lanes: int, prompt: int, steps: int, warmup: int, dist, sa
         cur = eng.decode_step(st, cur)
     fam = eng.profile_end()
     torch.cuda.synchronize()
+    # a kernel whose bounded wait ran out makes every later kernel return at once: such a run is
+    # fast and wrong, so it is no measurement
+    status = eng.status()
+    if status != 0:
+        raise RuntimeError(f"device status word is {status} after the timed steps at {lanes} lanes: "
+                           "a kernel gave up a bounded wait; no number is reported")
     st.close()
     total_ms = sum(v[0] for v in fam.values()) or 1.0
     return dict(lanes=lanes, ms_dev=ms_dev, steps_dev=steps_dev, ms_e2e=ms_e2e, steps_e2e=steps,
@@ -211,6 +217,8 @@ def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warm
     torch.cuda.synchronize()
     ms = a.elapsed_time(b)
     n = int(emitted.item())
+    if eng.status() != 0:
+        raise RuntimeError("device status word raised during the MTP rounds: no number is reported")
     m.close()
     st.close()
     return {"workload": f"configs[4]: {lanes} lanes x {prompt}-token chunk-64 prefill, {rounds} rounds of {depth} chained MTP "

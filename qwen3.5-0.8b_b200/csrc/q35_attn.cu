@@ -18,6 +18,8 @@
 // except that cached keys are bf16 (the engine's cache dtype, engine/state.h:90).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "q35_common.cuh"
 
 namespace q35 {
@@ -454,6 +456,279 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Cluster form for bodies of few rows: a thread-block cluster of CS CTAs shares one (row, kv head).
+// CTA `rank` takes the pages i = rank, rank + CS, ... of the lane's context, so a 560-position
+// context is read by 8 CTAs at once instead of one CTA walking 18 tiles.  The rounding points of the
+// single-CTA form are kept: scores f32; ONE softmax over the whole row - every CTA publishes its
+// local (max, sum of exp), all combine them in rank order to the row's max M and sum L, and the
+// weights bf16(exp(s - M) / L) are final before P.V; the f32 partial outputs are summed through
+// distributed shared memory in rank order (rank r sums and stores its 256 / CS slice of the dims).
+// Every CTA runs the same three cluster barriers whatever happens (a dead status word, an expired
+// wait): nothing in a cluster ever waits for a CTA that left early.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();                      // the aligned barrier needs the whole warp at this instruction
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t peer_addr(const void* p, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(smem_u32(p)), "r"(rank));
+    return ra;
+}
+__device__ __forceinline__ float peer_ld_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ float2 peer_ld_f32x2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];\n" : "=f"(v.x), "=f"(v.y) : "r"(addr) : "memory");
+    return v;
+}
+
+template <bool FUSED_APPEND>
+__global__ void __launch_bounds__(kTmaThreads, 2)
+attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * kRing];
+    __shared__ float ml_s[8];                              // local max [4 heads] | local sum of exp [4]
+    __shared__ float ML_s[8];                              // the row's max | 1 / sum
+    __shared__ __align__(16) float o_part[4 * kHeadDim];   // this CTA's f32 partial of P.V
+    pdl_wait();
+    const bool dead = p.status != nullptr && *p.status != 0;
+
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    float* q_s = reinterpret_cast<float*>(base_ptr + kRing * kTileBytes);      // [4][256]
+    float* sc2 = q_s + 4 * kHeadDim;                                           // [2][4][ctx_pad]
+    uint16_t* w_s = reinterpret_cast<uint16_t*>(sc2 + 8 * ctx_pad);            // [4][ctx_pad] bf16
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kRing]);
+
+    const int row = blockIdx.x, kvh = blockIdx.y, rank = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    const int g = ln >> 2, t = ln & 3;
+    const int lane_id = row / p.T, tt = row % p.T;
+    const int cap = p.pages_per_lane * kKvPage;
+    int slot = p.slot[lane_id] + tt;
+    const int rope_pos = p.rope_pos[lane_id] + tt;
+    const bool in_cap = slot < cap && slot < ctx_pad;
+    if (!in_cap) slot = (cap < ctx_pad ? cap : ctx_pad) - 1;
+    const int n_ctx = slot + 1;
+    const int P = (n_ctx + kKvPage - 1) / kKvPage;                       // pages of the whole context
+    const int myP = dead ? 0 : (P > rank ? (P - rank + cs - 1) / cs : 0); // pages this CTA reads: rank + j * cs
+    const bool owner = ((P - 1) % cs) == rank;                           // this CTA's last page holds the new row
+    const int* table = p.page_table + (size_t)lane_id * p.table_lane_stride;
+    const uint16_t* pr = p.proj + (size_t)row * kAttnProjN;
+
+    if (tid == 0) {
+        for (int b = 0; b < kRing; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(full0 + 8 * b) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;\n" ::"r"(empty0 + 8 * b) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    // tile j of 2 * myP: this CTA's K pages, then its V pages
+    auto issue = [&](int j) -> bool {
+        const int b = j % kRing;
+        const uint32_t ph = (j / kRing) & 1;
+        if (!mbar_wait(empty0 + 8 * b, ph ^ 1)) return false;
+        const int page = table[rank + (j < myP ? j : j - myP) * cs];
+        const CUtensorMap* map = j < myP ? &kmap : &vmap;
+        const uint32_t dst = ring + b * kTileBytes;
+        const int r0 = page * (kKvHeads * kKvPage) + kvh * kKvPage;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full0 + 8 * b), "r"(kTileBytes) : "memory");
+#pragma unroll
+        for (int cb = 0; cb < 4; ++cb)
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                ::"r"(dst + cb * 8192), "l"(reinterpret_cast<uint64_t>(map)), "r"(full0 + 8 * b), "r"(cb * 64), "r"(r0) : "memory");
+        return true;
+    };
+
+    // ---- prologue: the producer starts the pages that do not hold the new row; q / k / v prep -------
+    int issued = 0;
+    bool prod_ok = true;
+    if (warp == 8) {
+        if (ln == 0) {
+            const int safe = (FUSED_APPEND && owner) ? (myP - 1) : 2 * myP;
+            while (issued < kRing && issued < safe && prod_ok) { prod_ok = issue(issued); ++issued; }
+        }
+    } else if (warp < 4) {
+        const int head = kvh * 4 + warp;
+        float x[8];
+        unpack8(*reinterpret_cast<const uint4*>(pr + head * 2 * kHeadDim + 8 * ln), x);
+        head_norm_rope(x, p.q_norm, ln, rope_pos, p.inv_freq);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) q_s[warp * kHeadDim + 8 * ln + e] = x[e];
+    } else if (FUSED_APPEND && warp < 6 && in_cap && owner && !dead) {
+        append_kv(p, pr, table, kvh, slot, rope_pos, warp - 4, ln);
+        __threadfence();
+        asm volatile("fence.proxy.async;\n" ::: "memory");       // the new row must be visible to the TMA reads below
+    }
+    __syncthreads();
+
+    bool ok = true;
+    float acc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+
+    if (warp == 8) {
+        if (ln == 0) {
+            // Only tiles whose ring slot pass 1 frees may be issued before the cluster barrier below:
+            // a later tile waits for a release of pass 2, which starts after that barrier.
+            const int before = (myP + kRing) < 2 * myP ? (myP + kRing) : 2 * myP;
+            while (issued < before && prod_ok) { prod_ok = issue(issued); ++issued; }
+        }
+    } else {
+        // ---- pass 1: scores of this CTA's pages.  warp = (16-position m-tile, 128-dim half) --------
+        const int mt = warp & 3, kh = warp >> 2;
+        uint32_t bhi[8][2], blo[8][2];
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                float v0 = 0.f, v1 = 0.f;
+                if (g < 4) {
+                    const int d = kh * 128 + ks * 16 + half * 8 + 2 * t;
+                    v0 = q_s[g * kHeadDim + d];
+                    v1 = q_s[g * kHeadDim + d + 1];
+                }
+                const float h0 = bfround(v0), h1 = bfround(v1);
+                bhi[ks][half] = pack_bf2(h0, h1);
+                blo[ks][half] = pack_bf2(v0 - h0, v1 - h1);
+            }
+        for (int j = 0; j < myP; ++j) {
+            const int b = j % kRing;
+            if (ok) ok = mbar_wait(full0 + 8 * b, (j / kRing) & 1);
+            const uint32_t tile = ring + b * kTileBytes;
+            float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                const int r = mt * 16 + (ln & 15);
+                ldsm_x4(a, tile + tile_off(r, kh * 16 + ks * 2 + (ln >> 4)));
+                mma_bf16(sacc, a[0], a[1], a[2], a[3], bhi[ks][0], bhi[ks][1]);
+                mma_bf16(sacc, a[0], a[1], a[2], a[3], blo[ks][0], blo[ks][1]);
+            }
+            if (t < 2) {
+                const int pos = (rank + j * cs) * kKvPage + mt * 16 + g;
+                float* s0 = sc2 + (kh * 4 + 2 * t) * ctx_pad;
+                if (pos < ctx_pad) { s0[pos] = sacc[0] * 0.0625f; s0[ctx_pad + pos] = sacc[1] * 0.0625f; }
+                if (pos + 8 < ctx_pad) { s0[pos + 8] = sacc[2] * 0.0625f; s0[ctx_pad + pos + 8] = sacc[3] * 0.0625f; }
+            }
+            __syncwarp();
+            if (ln == 0) mbar_arrive(empty0 + 8 * b);
+        }
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        // ---- local max and sum of exp per head over this CTA's positions ----------------------------
+        if (warp < 4) {
+            const float* sa = sc2 + warp * ctx_pad;
+            const float* sb = sc2 + (4 + warp) * ctx_pad;
+            float m = -INFINITY;
+            for (int j = 0; j < myP; ++j) {
+                const int base = (rank + j * cs) * kKvPage;
+                for (int i = base + ln; i < base + kKvPage && i < n_ctx; i += 32) m = fmaxf(m, sa[i] + sb[i]);
+            }
+            m = warp_max(m);
+            float l = 0.f;
+            for (int j = 0; j < myP; ++j) {
+                const int base = (rank + j * cs) * kKvPage;
+                for (int i = base + ln; i < base + kKvPage && i < n_ctx; i += 32) l += expf(sa[i] + sb[i] - m);
+            }
+            l = warp_sum(l);
+            if (ln == 0) { ml_s[warp] = m; ml_s[4 + warp] = l; }
+        }
+    }
+    cluster_sync_all();                                    // (1) every CTA's (max, sum) is published
+
+    if (warp == 8 && ln == 0) {
+        while (issued < 2 * myP && prod_ok) { prod_ok = issue(issued); ++issued; }
+        if (!prod_ok && p.status != nullptr) atomicExch(p.status, 5);
+    }
+    if (warp < 4) {
+        // the row's max and sum, combined in rank order: identical in every CTA of the cluster
+        float M = -INFINITY;
+        for (int r = 0; r < cs; ++r) M = fmaxf(M, peer_ld_f32(peer_addr(&ml_s[warp], r)));
+        float L = 0.f;
+        for (int r = 0; r < cs; ++r) {
+            const float mr = peer_ld_f32(peer_addr(&ml_s[warp], r)), lr = peer_ld_f32(peer_addr(&ml_s[4 + warp], r));
+            if (lr > 0.f) L += lr * expf(mr - M);
+        }
+        const float* sa = sc2 + warp * ctx_pad;
+        const float* sb = sc2 + (4 + warp) * ctx_pad;
+        uint16_t* w = w_s + warp * ctx_pad;
+        for (int j = 0; j < myP; ++j) {
+            const int base = (rank + j * cs) * kKvPage;
+            for (int i = base + ln; i < base + kKvPage && i < ctx_pad; i += 32)
+                w[i] = i < n_ctx ? f2bf(__fdiv_rn(expf(sa[i] + sb[i] - M), L)) : (uint16_t)0;
+        }
+    }
+    if (warp < 8) {
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        // ---- pass 2: P.V over this CTA's pages.  warp = 32 output dims; heads ride in rows 0..3 -----
+        for (int j = 0; j < myP; ++j) {
+            const int tj = myP + j, b = tj % kRing;
+            if (ok) ok = mbar_wait(full0 + 8 * b, (tj / kRing) & 1);
+            const uint32_t tile = ring + b * kTileBytes;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+                const int p0 = (rank + j * cs) * kKvPage + ks * 16;
+                uint32_t a0 = 0, a2 = 0;
+                if (g < 4 && p0 + 16 <= ctx_pad) {
+                    a0 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 2 * t);
+                    a2 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 8 + 2 * t);
+                }
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    uint32_t r[4];
+                    const int pos = ks * 16 + (ln & 7) + ((ln >> 3) & 1) * 8;
+                    ldsm_x4_trans(r, tile + tile_off(pos, warp * 4 + np * 2 + (ln >> 4)));
+                    mma_bf16(acc[2 * np], a0, 0u, a2, 0u, r[0], r[1]);
+                    mma_bf16(acc[2 * np + 1], a0, 0u, a2, 0u, r[2], r[3]);
+                }
+            }
+            __syncwarp();
+            if (ln == 0) mbar_arrive(empty0 + 8 * b);
+        }
+        if (!ok && ln == 0 && p.status != nullptr) atomicExch(p.status, 6);
+        if (g < 4) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int dd = warp * 32 + nt * 8 + 2 * t;
+                *reinterpret_cast<float2*>(&o_part[g * kHeadDim + dd]) = make_float2(acc[nt][0], acc[nt][1]);
+            }
+        }
+    }
+    cluster_sync_all();                                    // (2) every CTA's partial output is published
+
+    // ---- rank r sums dims [r * DS, (r + 1) * DS) of the four heads in rank order, gates, stores -----
+    {
+        const int DS = kHeadDim / cs;
+        const bool alive = !dead && (p.status == nullptr || *p.status == 0);
+        if (tid < 2 * DS && alive) {
+            const int hh = tid / (DS / 2), dd = rank * DS + 2 * (tid % (DS / 2));
+            float2 sum = make_float2(0.f, 0.f);
+            for (int r = 0; r < cs; ++r) {
+                const float2 v = peer_ld_f32x2(peer_addr(&o_part[hh * kHeadDim + dd], r));
+                sum.x += v.x; sum.y += v.y;
+            }
+            const int head = kvh * 4 + hh;
+            const uint32_t gw = *reinterpret_cast<const uint32_t*>(pr + head * 2 * kHeadDim + kHeadDim + dd);
+            const float o0 = bfround(sum.x) * bfround(sigmoid_acc(lo_bf(gw)));
+            const float o1 = bfround(sum.y) * bfround(sigmoid_acc(hi_bf(gw)));
+            *reinterpret_cast<uint32_t*>(p.out + (size_t)row * (kQHeads * kHeadDim) + head * kHeadDim + dd) = pack_bf2(o0, o1);
+        }
+    }
+    cluster_sync_all();                                    // (3) no CTA leaves while a peer may still read it
+}
+
 size_t attn_tma_smem(int ctx_pad) {
     return 1024 + (size_t)kRing * kTileBytes + 4 * kHeadDim * 4 + (size_t)8 * ctx_pad * 4 + (size_t)4 * ctx_pad * 2;
 }
@@ -502,6 +777,10 @@ cudaError_t attn_init() {
     const int tma_bytes = (int)attn_tma_smem(kAttnTmaMaxCtx);
     e = cudaFuncSetAttribute(attn_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(attn_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(attn_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(attn_tma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
 }
 
@@ -524,6 +803,44 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
         }
         const int pad64 = (p.max_ctx + 63) & ~63;           // whole pages
         const size_t smem = attn_tma_smem(pad64);
+        // few lanes: a cluster of CTAs per (row, kv head) splits the context by pages.  The cluster
+        // size follows the LANE count, not the row count, so a one-token step and a multi-token
+        // verify body of the same lanes sum in the same order.
+        static int cluster_mode = -1;
+        if (cluster_mode < 0) {
+            const char* env = std::getenv("Q35_ATTN_CLUSTER");
+            cluster_mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+        }
+        int cs = 1;
+        if (cluster_mode) {
+            cs = p.lanes <= 8 ? 8 : (p.lanes <= 32 ? 4 : 1);      // measured: no gain from 64 lanes up
+            static int forced = -1;                      // tuning knob: Q35_ATTN_CS = 1, 2, 4 or 8
+            if (forced < 0) {
+                const char* env = std::getenv("Q35_ATTN_CS");
+                forced = env != nullptr ? std::atoi(env) : 0;
+                if (forced != 1 && forced != 2 && forced != 4 && forced != 8) forced = 0;
+            }
+            if (forced) cs = forced;
+            while (cs > pad64 / kKvPage) cs >>= 1;
+        }
+        if (cs > 1) {
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(rows, kKvHeads, cs);
+            cfg.blockDim = dim3(kTmaThreads);
+            cfg.dynamicSmemBytes = smem;
+            cfg.stream = st;
+            cudaLaunchAttribute at[2];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 1;
+            at[0].val.clusterDim.y = 1;
+            at[0].val.clusterDim.z = cs;
+            at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = at;
+            cfg.numAttrs = pdl_enabled() ? 2 : 1;
+            if (p.T == 1) return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true>, p, pad64, cs, kmap, vmap);
+            return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false>, p, pad64, cs, kmap, vmap);
+        }
         if (p.T == 1) return launch_k(attn_tma_kernel<true>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
         return launch_k(attn_tma_kernel<false>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
     }
