@@ -108,8 +108,8 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
 }
 
 // K-split form: one CTA of 128 threads per row, 8 elements per thread, so the n_split f32 partial
-// rows (4 KiB each) are pulled by many CTAs at once; the partial loads of four splits are in flight
-// together.  Same arithmetic as add_norm_kernel (partials summed in split order, one bf16 rounding).
+// rows (4 KiB each) are pulled by many CTAs at once; the partial loads of up to eight splits are in flight
+// together (eight, then four, then one).  Same arithmetic as add_norm_kernel (partials summed in split order, one bf16 rounding).
 __global__ void __launch_bounds__(128)
 add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ parts, int n_split,
                       const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
@@ -123,6 +123,19 @@ add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ 
     const float* pp = parts + (size_t)row * kHidden + off;
     const size_t zs = (size_t)rows * kHidden;
     int z = 0;
+    for (; z + 8 <= n_split; z += 8) {       // eight splits in flight: one round trip for most split counts
+        float4 p[8][2];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            p[u][0] = *reinterpret_cast<const float4*>(pp + (z + u) * zs);
+            p[u][1] = *reinterpret_cast<const float4*>(pp + (z + u) * zs + 4);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            acc[0] += p[u][0].x; acc[1] += p[u][0].y; acc[2] += p[u][0].z; acc[3] += p[u][0].w;
+            acc[4] += p[u][1].x; acc[5] += p[u][1].y; acc[6] += p[u][1].z; acc[7] += p[u][1].w;
+        }
+    }
     for (; z + 4 <= n_split; z += 4) {
         float4 p[4][2];
 #pragma unroll
