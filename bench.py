@@ -46,7 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 GDN_BYTES_PER_LANE_LAYER = 2 * 1048576 + 98304 + 12288 + 4096 + 4096
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gdn_step_kernel, from the ncu capture
 # summarised in profiles/ (per lane; scaled by the lanes of a launch).  None until captured.
-GDN_NCU_TRAFFIC_PER_LANE = 2.010e6      # profiles/gdn_step_kernel_256_lanes.md: 514.6 MB per launch of 256 lanes
+GDN_NCU_TRAFFIC_PER_LANE = 1.979e6      # dram read + write per lane per launch, ncu capture at 256 lanes (profiles/gdn_step_kernel_256_lanes.md); grows in proportion to lanes
 
 
 def peaks():
@@ -55,6 +55,25 @@ def peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return FALLBACK_HBM_GBS, "fallback (6650 GB/s, earlier measurement on this pool)"
+
+
+def live_copy_gbs() -> float:
+    """STREAM-style copy bandwidth of THIS GPU, measured the way MEASURED_PEAKS.json's figure was
+    (b.copy_(a) over 1 Gi bf16 elements, read + write bytes, best of 5, CUDA events).  Reported beside
+    the roofline so that GPU-to-GPU spread in the pool can be told from a change in the kernels."""
+    n = 1 << 30
+    a = torch.empty(n, dtype=torch.bfloat16, device="cuda").fill_(1.0)
+    b = torch.empty_like(a)
+    best = 0.0
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        b.copy_(a)
+        e1.record()
+        torch.cuda.synchronize()
+        best = max(best, 4.0 * n / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del a, b
+    return round(best, 1)
 
 
 class ClockSampler:
@@ -359,6 +378,10 @@ def main():
            "gpu_launches": eng.census()["launches_decode" if args.lanes > 16 else "launches_decode_few_lanes"] * m["steps_dev"],
            "clocks": m["clocks"], "roofline": roofline_of(eng, m), "prefill_s": round(m["prefill_s"], 2),
            "prefill_tok_per_s": round(args.lanes * args.prompt / m["prefill_s"], 1)}
+    if rank == 0:
+        # after the timed regions, with the lanes' state freed: this GPU's own copy bandwidth
+        out["roofline"]["copy_gbs_this_gpu"] = live_copy_gbs()
+        out["roofline"]["frac_of_this_gpu"] = round(out["roofline"]["achieved"] / out["roofline"]["copy_gbs_this_gpu"], 4)
     sweep = []
     if rank == 0 and args.sweep:
         for L in [int(x) for x in args.sweep.split(",") if x]:

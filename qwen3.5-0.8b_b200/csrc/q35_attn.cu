@@ -814,6 +814,7 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
         int cs = 1;
         if (cluster_mode) {
             cs = p.lanes <= 8 ? 8 : (p.lanes <= 32 ? 4 : 1);      // measured: no gain from 64 lanes up
+            if (p.T > 4) cs = 1;                                 // prompt bodies bring their own parallelism
             static int forced = -1;                      // tuning knob: Q35_ATTN_CS = 1, 2, 4 or 8
             if (forced < 0) {
                 const char* env = std::getenv("Q35_ATTN_CS");
