@@ -299,7 +299,12 @@ def paged(K, V, pages_per_lane, lanes):
     return kpool, vpool, table
 
 
-@pytest.mark.parametrize("ctxs", [[0], [1], [37], [63, 64, 65], [511, 512, 513], [2, 200]])
+@pytest.mark.parametrize("ctxs", [[0], [1], [37], [63, 64, 65], [511, 512, 513], [2, 200],
+                                  # 9-32 lanes: clusters of 4 CTAs, up to 4 pages per CTA (more than the 2-deep ring)
+                                  [513, 600, 64, 1, 200, 700, 511, 37, 128, 129, 640, 333],
+                                  [1000, 3, 960, 448, 0, 77, 831, 512, 640],
+                                  # more than 32 lanes: the single-CTA form
+                                  [17 * i % 300 for i in range(40)]])
 def test_attn_decode_vs_oracle(eng, weights, ctxs):
     """Ragged contexts, page-boundary contexts, empty cache.  The oracle here caches bf16 keys
     like the engine; the difference to the reference's f32-key cache is covered by the golden
