@@ -340,6 +340,41 @@ def test_attn_decode_vs_oracle(eng, weights, ctxs):
         assert torch.equal(vd[pg, :, c % 64], refs[i][2])
 
 
+def test_attn_long_context_form(eng, weights):
+    """Contexts beyond 1,024 positions (the plain-load kernel; up to the 8,192-position cap) on
+    synthetic caches: keys with the scale the k-norm produces, values N(0, 1)."""
+    l = 3
+    pre = f"{O.LM}layers.{l}.self_attn."
+    ctxs = [1024, 1500, 4031, 8191]
+    lanes = len(ctxs)
+    gen = torch.Generator().manual_seed(99)
+    Ks, Vs, projs, refs = [], [], [], []
+    for c in ctxs:
+        K = (torch.randn((c, 2, 256), generator=gen) * 2.0).to(torch.bfloat16).float()
+        V = torch.randn((c, 2, 256), generator=gen).to(torch.bfloat16)
+        kv = {"k": [K], "v": [V]}
+        hq = torch.randn((1, 1024), generator=gen).to(torch.bfloat16)
+        d = {}
+        O.attn_mixer(weights, pre, hq, c, kv, True, d)
+        Ks.append(K); Vs.append(V)
+        refs.append((d["gated"], torch.cat(kv["k"], 0)[-1], torch.cat(kv["v"], 0)[-1]))
+        projs.append(torch.cat([d["qg"].reshape(1, -1), d["k_raw"].reshape(1, -1), d["v_raw"].reshape(1, -1)], -1))
+    ppl = max(ctxs) // 64 + 1
+    kpool, vpool, table = paged(Ks, Vs, ppl, lanes)
+    kd, vd = cu(kpool), cu(vpool)
+    out = eng.op_attn_decode(cu(torch.cat(projs, 0)), cu(weights[pre + "q_norm.weight"]),
+                             cu(weights[pre + "k_norm.weight"]), kd, vd, cu(table),
+                             cu(torch.tensor(ctxs, dtype=torch.int32)), lanes).cpu()
+    kd, vd = kd.cpu(), vd.cpu()
+    for i, c in enumerate(ctxs):
+        e = rel_l2(out[i].float(), refs[i][0].float())
+        assert e <= 1e-2, (c, e)
+        pg = int(table[i, c // 64])
+        assert rel_l2(kd[pg, :, c % 64].float(), refs[i][1]) < 2e-3
+        assert torch.equal(vd[pg, :, c % 64], refs[i][2])
+        note(f"attn_long_ctx{c}_rel_l2", e)
+
+
 def test_attn_golden(eng, weights, golden):
     """Decode row at position 37 on the reference's own cache (f32 keys rounded to bf16 for the
     engine): pre-o_proj gated rows within 1e-2 of the reference's."""
