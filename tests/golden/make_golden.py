@@ -49,7 +49,7 @@ def top2(row_f32):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of erokhins/qwen3.5-0.8b (its speccheck/ package is imported)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     from speccheck import mtp as ref_mtp          # noqa: E402

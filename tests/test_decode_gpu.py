@@ -6,8 +6,8 @@ End-to-end numbers are cascade numbers: the reference's own legal variants (chun
 recurrent prefill, one-pass vs online softmax) differ by 3-7e-2 rel-L2 in the final logits on
 these random-init weights, because 1-ULP bf16 differences are amplified through 24 residual
 layers.  The 1e-2 / 1e-4 contract is asserted per stage with shared inputs in test_ops_gpu.py;
-here the cascade is held under 8e-2 and its measured value is written to
-gpurun_out/parity_decode.json.
+here the cascade is held under 8e-2 and its measured value is written to parity_decode.json in
+the run's output folder.
 """
 from __future__ import annotations
 

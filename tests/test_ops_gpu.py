@@ -342,7 +342,7 @@ def test_attn_decode_vs_oracle(eng, weights, ctxs):
 
 def test_attn_long_context_form(eng, weights):
     """Contexts beyond 1,024 positions (the plain-load kernel; up to the 8,192-position cap) on
-    synthetic caches: keys with the scale the k-norm produces, values N(0, 1)."""
+    synthetic caches (keys N(0, 0.25), values N(0, 1): thousands of positions carry weight)."""
     l = 3
     pre = f"{O.LM}layers.{l}.self_attn."
     ctxs = [1024, 1500, 4031, 8191]
@@ -350,7 +350,7 @@ def test_attn_long_context_form(eng, weights):
     gen = torch.Generator().manual_seed(99)
     Ks, Vs, projs, refs = [], [], [], []
     for c in ctxs:
-        K = (torch.randn((c, 2, 256), generator=gen) * 2.0).to(torch.bfloat16).float()
+        K = (torch.randn((c, 2, 256), generator=gen) * 0.5).to(torch.bfloat16).float()     # score std ~1: a broad softmax
         V = torch.randn((c, 2, 256), generator=gen).to(torch.bfloat16)
         kv = {"k": [K], "v": [V]}
         hq = torch.randn((1, 1024), generator=gen).to(torch.bfloat16)
