@@ -454,7 +454,7 @@ extern "C" int q35_step_census(const q35_engine* e, q35_census* out) {
     params += (long long)e->vocab * kHidden;
     out->flops_per_row = 2 * params;
     out->launches_decode = 1 + kLayers * 7 + 3;
-    out->launches_decode_few_lanes = kSmallStepLaunches;
+    out->launches_decode_few_lanes = e->small_step_enabled ? kSmallStepLaunches : out->launches_decode;
     return Q35_OK;
 }
 
