@@ -5,10 +5,14 @@
 // items of a layer.  Everything the NEXT item needs from HBM - its 64 KiB head state, its q/k/v
 // rows, conv window rows and z row - is fetched into shared memory by bulk async copies
 // (cp.async.bulk, completion on one mbarrier) while the current item is updated, so every SM keeps
-// state loads in flight all the time and no global-load latency sits on an item's critical path.  The current tile lives in registers (thread = 16 rows x 4 columns): both reductions of the
+// state loads in flight all the time and no global-load latency sits on an item's critical path.
+// The current tile lives in registers (thread = 16 rows x 4 columns): both reductions of the
 // update (r = S^T k and o = S^T q) run on the register copy with a cross-warp shared-memory reduce,
 // and the new state is written back exactly once with 16-byte stores.  This is the HBM term that
 // dominates the step at high lane counts (2 x 1 MiB per layer per lane).
+// What every warp must do per item is one chain (copy, conv, pass 1, pass 2, stores); everything
+// else is given to warps that would otherwise idle in the conv stage (see the kernel's comment), so
+// that the chain, not one overloaded warp, sets the pace and two CTAs per SM saturate HBM.
 // The mbarrier wait is bounded (about one second of polling): on expiry the kernel raises the
 // status word it was given and returns.
 //
@@ -57,37 +61,52 @@ constexpr uint32_t kInBytes = kInRows * 128 * sizeof(uint16_t);
 constexpr uint32_t kFetchBytes = kTileBytes + kInBytes;
 constexpr size_t kGdnSmemBytes = kTileBytes + kInBytes;
 
-// One thread: everything item (lane_id, h) needs from HBM for its first token, as bulk copies that
-// complete on one mbarrier: the 64 KiB state tile and thirteen 256-byte rows of small inputs.
-// Two parts: the state tile and conv window (written by this layer's previous step only) and the
-// rows of this step's projection; the first may be issued before the projection kernel has ended.
-__device__ __forceinline__ void item_fetch_state(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
-                                                 uint32_t in_addr, uint32_t bar) {
+// Everything item (lane_id, h) needs from HBM for its first token, as bulk copies that complete on
+// one mbarrier: the 64 KiB state tile and thirteen 256-byte rows of small inputs.  The fourteen
+// copies are issued by fourteen lanes of one warp at once (`part` = lane): 0 = expect_tx + tile,
+// 1..3 = raw q, k, v rows, 4..12 = window rows, 13 = z row.  `what` bit 0: the state tile and conv
+// window (written by this layer's previous step only), bit 1: the rows of this step's projection;
+// the first may be issued before the projection kernel ahead of this one has ended.
+// Every lane of the warp must call this (it contains a warp barrier).
+__device__ __forceinline__ void item_fetch_part(const GdnParams& p, int lane_id, int h, int part, int what,
+                                                uint32_t tile_addr, uint32_t in_addr, uint32_t bar) {
     const int sel = p.sel != nullptr ? p.sel[lane_id] : 0;
-    const float* S = pick_buf(p.S, sel) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
-    const uint16_t* win = pick_buf(p.win, sel) + (size_t)lane_id * 3 * kConvCh;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
-    bulk_g2s(tile_addr, S, kTileBytes, bar);
-#pragma unroll
-    for (int kind = 0; kind < 3; ++kind)
-#pragma unroll
-        for (int j = 0; j < 3; ++j)
+    if (what & 1) {
+        if (part == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
+            bulk_g2s(tile_addr, pick_buf(p.S, sel) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv), kTileBytes, bar);
+        }
+        __syncwarp();                      // the transaction count is armed before any other copy can land
+        if (part >= 4 && part <= 12) {
+            const int j = (part - 4) / 3, kind = (part - 4) % 3;
+            const uint16_t* win = pick_buf(p.win, sel) + (size_t)lane_id * 3 * kConvCh;
             bulk_g2s(in_addr + (3 + j * 3 + kind) * 256, win + j * kConvCh + kind * 2048 + h * 128, 256, bar);
-}
-__device__ __forceinline__ void item_fetch_rows(const GdnParams& p, int lane_id, int h, uint32_t in_addr,
-                                                uint32_t bar) {
-    const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
-#pragma unroll
-    for (int kind = 0; kind < 3; ++kind) bulk_g2s(in_addr + kind * 256, pr + kind * 2048 + h * 128, 256, bar);
-    bulk_g2s(in_addr + 12 * 256, pr + kOffZ + h * 128, 256, bar);
-}
-__device__ __forceinline__ void item_fetch(const GdnParams& p, int lane_id, int h, uint32_t tile_addr,
-                                           uint32_t in_addr, uint32_t bar) {
-    item_fetch_state(p, lane_id, h, tile_addr, in_addr, bar);
-    item_fetch_rows(p, lane_id, h, in_addr, bar);
+        }
+    }
+    if (what & 2) {
+        const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
+        if (part >= 1 && part <= 3) bulk_g2s(in_addr + (part - 1) * 256, pr + (part - 1) * 2048 + h * 128, 256, bar);
+        if (part == 13) bulk_g2s(in_addr + 12 * 256, pr + kOffZ + h * 128, 256, bar);
+    }
 }
 
+// conv taps stay packed as two bf16 pairs; f32 taps in ascending order, one bf16 rounding, SiLU in bf16
+__device__ __forceinline__ float conv_silu(float (&w)[3], float raw, uint2 tap) {
+    float acc = __fmul_rn(w[0], lo_bf(tap.x));
+    acc = __fadd_rn(acc, __fmul_rn(w[1], hi_bf(tap.x)));
+    acc = __fadd_rn(acc, __fmul_rn(w[2], lo_bf(tap.y)));
+    acc = __fadd_rn(acc, __fmul_rn(raw, hi_bf(tap.y)));
+    w[0] = w[1]; w[1] = w[2]; w[2] = raw;
+    return bfround(silu_acc(bfround(acc)));
+}
+
+// Warp roles.  Warps 0-3 (thread = channel c): conv of q and v.  Warps 4-7 (thread = channel /
+// column c): conv of k, the gated RMSNorm of column c, and - warp 4 - the fetch of the next item.
+// The gated norm of an item's last token is DEFERRED: it runs after the next item's tile has been
+// copied to registers, in the shadow of that item's conv (which warps 0-3 carry the longer half
+// of), so neither the norm nor the fetch sits on the chain conv -> pass 1 -> pass 2 -> stores that
+// every warp walks.
 __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     float* tile = reinterpret_cast<float*>(dyn_smem);                          // 128x128 f32 head tile
@@ -97,30 +116,35 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     __shared__ __align__(16) float red_r[8][128];
     __shared__ __align__(16) float red_o[8][128];
     __shared__ float ssum[4][2];
+    __shared__ float osum[4];
     __shared__ float scal_s[2];
 
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    const bool is_qv = tid < 128, issuer = warp == 4;
+    const int c = tid & 127;
     // the grid is a multiple of 16, so a CTA keeps one head and strides over lanes
     const int h = blockIdx.x % kGdnHeads;
     const int lane_stride = gridDim.x / kGdnHeads;
     const uint32_t bar = smem_u32(&bar_storage);
     const uint32_t tile_addr = smem_u32(tile), in_addr = smem_u32(in_s);
-    float nb_raw = 0.f, na_raw = 0.f;          // thread 0: gate inputs of the item being fetched
+    float nb_raw = 0.f, na_raw = 0.f;          // warp 4, lane 0: gate inputs of the item being fetched
     {
-        // the first state tile is on its way before the projection kernel ahead of this one has ended
         const int l0 = blockIdx.x / kGdnHeads;
         if (tid == 0) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar) : "memory");
             asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-            if (l0 < p.lanes) item_fetch_state(p, l0, h, tile_addr, in_addr, bar);
         }
-        pdl_wait();
         __syncthreads();
-        if (tid == 0 && l0 < p.lanes) {
-            item_fetch_rows(p, l0, h, in_addr, bar);
-            const uint16_t* pr0 = p.proj + (size_t)l0 * p.T * kGdnProjN;
-            nb_raw = bf2f(pr0[kOffB + h]);
-            na_raw = bf2f(pr0[kOffA + h]);
+        // the first state tile is on its way before the projection kernel ahead of this one has ended
+        if (issuer && l0 < p.lanes) item_fetch_part(p, l0, h, ln, 1, tile_addr, in_addr, bar);
+        pdl_wait();
+        if (issuer && l0 < p.lanes) {
+            item_fetch_part(p, l0, h, ln, 2, tile_addr, in_addr, bar);
+            if (ln == 0) {
+                const uint16_t* pr0 = p.proj + (size_t)l0 * p.T * kGdnProjN;
+                nb_raw = bf2f(pr0[kOffB + h]);
+                na_raw = bf2f(pr0[kOffA + h]);
+            }
         }
     }
 
@@ -128,24 +152,30 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     const float negA = -expf(bf2f(p.A_log[h]));
     const float dtb = bf2f(p.dt_bias[h]);
     const float q_scale = 0.08838834764831845f;   // 128^-1/2
-    float tap[3][4];
-    int ch[3] = {0, 0, 0};
-    if (tid < 128) {
+    const int chA = (is_qv ? 0 : 2048) + h * 128 + c;          // q or k channel of this thread
+    const int chB = 4096 + h * 128 + c;                        // v channel (warps 0-3)
+    const uint2 tapA = *reinterpret_cast<const uint2*>(p.conv_w + (size_t)chA * 4);
+    const uint2 tapB = *reinterpret_cast<const uint2*>(p.conv_w + (size_t)chB * 4);
+    const float nw = bf2f(p.norm_w[c]);
+
+    // gated RMSNorm of column c over the head's 128 outputs (f32 until the single bf16 cast); warps 4-7
+    auto gated_norm = [&](float z, size_t row) {
+        float o = 0.f;
 #pragma unroll
-        for (int kind = 0; kind < 3; ++kind) {
-            ch[kind] = kind * 2048 + h * 128 + tid;
-            const uint2 tw = *reinterpret_cast<const uint2*>(p.conv_w + (size_t)ch[kind] * 4);
-            tap[kind][0] = lo_bf(tw.x); tap[kind][1] = hi_bf(tw.x);
-            tap[kind][2] = lo_bf(tw.y); tap[kind][3] = hi_bf(tw.y);
-        }
-    }
-    float nw4[4] = {0.f, 0.f, 0.f, 0.f};
-    if (warp == 0) {
-        const uint2 nv = *reinterpret_cast<const uint2*>(p.norm_w + 4 * ln);
-        nw4[0] = lo_bf(nv.x); nw4[1] = hi_bf(nv.x); nw4[2] = lo_bf(nv.y); nw4[3] = hi_bf(nv.y);
-    }
+        for (int w = 0; w < 8; ++w) o += red_o[w][c];
+        const float oo = warp_sum(o * o);
+        if (ln == 0) osum[warp - 4] = oo;
+        asm volatile("bar.sync 3, 128;\n" ::: "memory");
+        const float ms = (osum[0] + osum[1] + osum[2] + osum[3]) * (1.0f / 128.0f);
+        float n = __fmul_rn(o, rsqrt_acc(ms + kEps));
+        n = __fmul_rn(nw, n);
+        p.y[row * kValueDim + h * 128 + c] = f2bf(__fmul_rn(n, silu_acc(z)));
+    };
 
     uint32_t phase = 0;
+    bool pend = false;                         // warps 4-7: a gated norm is owed for (row_pend, z_pend)
+    size_t row_pend = 0;
+    float z_pend = 0.f;
     for (int lane_id = blockIdx.x / kGdnHeads; lane_id < p.lanes; lane_id += lane_stride) {
         const int sel = p.sel != nullptr ? p.sel[lane_id] : 0;
         const size_t s_off = ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
@@ -154,7 +184,8 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
         uint16_t* win_live = pick_buf(p.win, sel) + w_off;
 
         // ---- prefetched tile and inputs: shared memory -> registers ------------------------------
-        if (!mbar_wait_bounded(bar, phase)) {
+        // one verdict for the whole CTA: nobody may leave while others go on to the barriers below
+        if (!__syncthreads_and(mbar_wait_bounded(bar, phase))) {
             if (tid == 0 && p.status != nullptr) atomicExch(p.status, 1);
             return;
         }
@@ -165,52 +196,57 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 #pragma unroll
             for (int r = 0; r < 16; ++r) s[r] = Sp[(warp * 16 + r) * 32 + ln];
         }
-        float raw0[3] = {0.f, 0.f, 0.f}, win[3][3];
-        uint2 z4 = make_uint2(0, 0);
-        if (warp == 0) z4 = *reinterpret_cast<const uint2*>(in_s + 12 * 128 + 4 * ln);
-        if (tid < 128) {
+        const int kindA = is_qv ? 0 : 1;
+        float rawA = bf2f(in_s[kindA * 128 + c]), rawB = bf2f(in_s[2 * 128 + c]);
+        float winA[3], winB[3];
 #pragma unroll
-            for (int kind = 0; kind < 3; ++kind) {
-                raw0[kind] = bf2f(in_s[kind * 128 + tid]);
-#pragma unroll
-                for (int j = 0; j < 3; ++j) win[kind][j] = bf2f(in_s[(3 + j * 3 + kind) * 128 + tid]);
-            }
+        for (int j = 0; j < 3; ++j) {
+            winA[j] = bf2f(in_s[(3 + j * 3 + kindA) * 128 + c]);
+            winB[j] = bf2f(in_s[(3 + j * 3 + 2) * 128 + c]);
         }
-        if (tid == 0) { scal_s[0] = nb_raw; scal_s[1] = na_raw; }
-        __syncthreads();                   // every thread has its copy: the buffers are free again
-        if (tid == 0) {
+        const float z_cur = bf2f(in_s[12 * 128 + c]);
+        if (tid == 128) { scal_s[0] = nb_raw; scal_s[1] = na_raw; }
+        // Every thread has its copy: the buffers are free again.  Only warp 4, which issues the next
+        // fetch, waits for that; the others announce it and go on.
+        if (issuer) {
+            asm volatile("bar.sync 2, 256;\n" ::: "memory");
             const int nxt = lane_id + lane_stride;
             if (nxt < p.lanes) {
-                item_fetch(p, nxt, h, tile_addr, in_addr, bar);
-                const uint16_t* prn = p.proj + (size_t)nxt * p.T * kGdnProjN;
-                nb_raw = bf2f(prn[kOffB + h]);
-                na_raw = bf2f(prn[kOffA + h]);
-            } else {
+                item_fetch_part(p, nxt, h, ln, 3, tile_addr, in_addr, bar);
+                if (ln == 0) {
+                    const uint16_t* prn = p.proj + (size_t)nxt * p.T * kGdnProjN;
+                    nb_raw = bf2f(prn[kOffB + h]);
+                    na_raw = bf2f(prn[kOffA + h]);
+                }
+            } else if (ln == 0) {
                 pdl_trigger();             // last item of this CTA: the next kernel may start its weight loads
             }
+        } else {
+            asm volatile("bar.arrive 2, 256;\n" ::: "memory");
+        }
+        // the previous item's gated norm, in the shadow of this item's conv
+        if (!is_qv && pend) {
+            gated_norm(z_pend, row_pend);
+            pend = false;
         }
 
         for (int t = 0; t < p.T; ++t) {
             const size_t row = (size_t)lane_id * p.T + t;
             const uint16_t* pr = p.proj + row * kGdnProjN;
 
-            // ---- conv (f32 taps in ascending order, one bf16 rounding) + SiLU in bf16 ---------
-            if (tid < 128) {
-                float u[3];
-#pragma unroll
-                for (int kind = 0; kind < 3; ++kind) {
-                    const float raw = (t == 0) ? raw0[kind] : bf2f(pr[ch[kind]]);
-                    float acc = __fmul_rn(win[kind][0], tap[kind][0]);
-                    acc = __fadd_rn(acc, __fmul_rn(win[kind][1], tap[kind][1]));
-                    acc = __fadd_rn(acc, __fmul_rn(win[kind][2], tap[kind][2]));
-                    acc = __fadd_rn(acc, __fmul_rn(raw, tap[kind][3]));
-                    u[kind] = bfround(silu_acc(bfround(acc)));
-                    win[kind][0] = win[kind][1]; win[kind][1] = win[kind][2]; win[kind][2] = raw;
+            // ---- conv + SiLU: q and v on warps 0-3, k on warps 4-7 -------------------------------
+            {
+                if (t > 0) { rawA = bf2f(pr[chA]); rawB = bf2f(pr[chB]); }
+                const float uA = conv_silu(winA, rawA, tapA);
+                const float sq = warp_sum(uA * uA);
+                if (is_qv) {
+                    q_s[c] = uA;
+                    v_s[c] = conv_silu(winB, rawB, tapB);
+                    if (ln == 0) ssum[warp][0] = sq;
+                } else {
+                    k_s[c] = uA;
+                    if (ln == 0) ssum[warp - 4][1] = sq;
                 }
-                q_s[tid] = u[0]; k_s[tid] = u[1]; v_s[tid] = u[2];
-                const float qq = warp_sum(u[0] * u[0]);
-                const float kk = warp_sum(u[1] * u[1]);
-                if (ln == 0) { ssum[warp][0] = qq; ssum[warp][1] = kk; }
             }
             __syncthreads();
 
@@ -262,31 +298,15 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
             *reinterpret_cast<float4*>(&red_o[warp][4 * ln]) = po;
             __syncthreads();
 
-            // ---- gated RMSNorm over the head's 128 outputs (f32 until the single bf16 cast) ----
-            // warp 0 alone: a lane takes 4 columns, so the mean square needs no block barrier and the
-            // other warps move on to their state stores / the next item
-            if (warp == 0) {
-                float4 o4 = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const float4 a = *reinterpret_cast<const float4*>(&red_o[w][4 * ln]);
-                    o4.x += a.x; o4.y += a.y; o4.z += a.z; o4.w += a.w;
+            // ---- gated RMSNorm: at once for a token that is not the item's last, else deferred ---
+            if (!is_qv) {
+                if (t + 1 < p.T) {
+                    gated_norm(bf2f(pr[kOffZ + h * 128 + c]), row);
+                } else {
+                    pend = true;
+                    row_pend = row;
+                    z_pend = (t == 0) ? z_cur : bf2f(pr[kOffZ + h * 128 + c]);
                 }
-                const float ms = warp_sum(o4.x * o4.x + o4.y * o4.y + o4.z * o4.z + o4.w * o4.w) * (1.0f / 128.0f);
-                const float rinv = rsqrt_acc(ms + kEps);
-                uint2 zr = z4;
-                if (t > 0) zr = *reinterpret_cast<const uint2*>(pr + kOffZ + h * 128 + 4 * ln);
-                const float zf[4] = {lo_bf(zr.x), hi_bf(zr.x), lo_bf(zr.y), hi_bf(zr.y)};
-                const float of[4] = {o4.x, o4.y, o4.z, o4.w};
-                float out[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float n = __fmul_rn(of[c], rinv);
-                    n = __fmul_rn(nw4[c], n);
-                    out[c] = __fmul_rn(n, silu_acc(zf[c]));
-                }
-                *reinterpret_cast<uint2*>(p.y + row * kValueDim + h * 128 + 4 * ln) =
-                    make_uint2(pack_bf2(out[0], out[1]), pack_bf2(out[2], out[3]));
             }
 
             // ---- checkpoint after every non-final token of a speculative verify body -------------
@@ -296,12 +316,11 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
                 float4* Sc = reinterpret_cast<float4*>(pick_buf(p.S, cb) + s_off);
 #pragma unroll
                 for (int r = 0; r < 16; ++r) Sc[(warp * 16 + r) * 32 + ln] = s[r];
-                if (tid < 128) {
-                    uint16_t* wc = pick_buf(p.win, cb) + w_off;
+                uint16_t* wc = pick_buf(p.win, cb) + w_off;
 #pragma unroll
-                    for (int kind = 0; kind < 3; ++kind)
-#pragma unroll
-                        for (int j = 0; j < 3; ++j) wc[j * kConvCh + ch[kind]] = f2bf(win[kind][j]);
+                for (int j = 0; j < 3; ++j) {
+                    wc[j * kConvCh + chA] = f2bf(winA[j]);
+                    if (is_qv) wc[j * kConvCh + chB] = f2bf(winB[j]);
                 }
             }
         }
@@ -311,13 +330,13 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
 #pragma unroll
             for (int r = 0; r < 16; ++r) So[(warp * 16 + r) * 32 + ln] = s[r];
         }
-        if (tid < 128) {
 #pragma unroll
-            for (int kind = 0; kind < 3; ++kind)
-#pragma unroll
-                for (int j = 0; j < 3; ++j) win_live[j * kConvCh + ch[kind]] = f2bf(win[kind][j]);
+        for (int j = 0; j < 3; ++j) {
+            win_live[j * kConvCh + chA] = f2bf(winA[j]);
+            if (is_qv) win_live[j * kConvCh + chB] = f2bf(winB[j]);
         }
     }
+    if (!is_qv && pend) gated_norm(z_pend, row_pend);      // the last item's norm
 }
 
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
