@@ -359,6 +359,8 @@ def main():
         td.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_package()
     pkg.build_lib.build()
+    # this GPU's own copy bandwidth, taken first, on an idle GPU, the way MEASURED_PEAKS.json's figure was
+    copy_gbs = live_copy_gbs() if rank == 0 else 0.0
     params = pkg.weights.make_weights(seed=0)
     # scratch rows: 64 prompt tokens per lane per prefill body (the chunk-64 GDN scan), capped at 256 Ki rows
     rows = max(min(64 * args.lanes, 262144), 2 * args.lanes, 1024)
@@ -379,9 +381,8 @@ def main():
            "clocks": m["clocks"], "roofline": roofline_of(eng, m), "prefill_s": round(m["prefill_s"], 2),
            "prefill_tok_per_s": round(args.lanes * args.prompt / m["prefill_s"], 1)}
     if rank == 0:
-        # after the timed regions, with the lanes' state freed: this GPU's own copy bandwidth
-        out["roofline"]["copy_gbs_this_gpu"] = live_copy_gbs()
-        out["roofline"]["frac_of_this_gpu"] = round(out["roofline"]["achieved"] / out["roofline"]["copy_gbs_this_gpu"], 4)
+        out["roofline"]["copy_gbs_this_gpu"] = copy_gbs
+        out["roofline"]["frac_of_this_gpu"] = round(out["roofline"]["achieved"] / copy_gbs, 4)
     sweep = []
     if rank == 0 and args.sweep:
         for L in [int(x) for x in args.sweep.split(",") if x]:
