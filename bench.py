@@ -46,7 +46,7 @@ FALLBACK_HBM_GBS = 6650.0
 GDN_BYTES_PER_LANE_LAYER = 2 * 1048576 + 98304 + 12288 + 4096 + 4096
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of gdn_step_kernel, from the ncu capture
 # summarised in profiles/ (per lane; scaled by the lanes of a launch).  None until captured.
-GDN_NCU_TRAFFIC_PER_LANE = 1.979e6      # dram read + write per lane per launch, ncu capture at 256 lanes (profiles/gdn_step_kernel_256_lanes.md); grows in proportion to lanes
+GDN_NCU_TRAFFIC_PER_LANE = 1.968e6      # dram read + write per lane per launch, ncu capture at 256 lanes (profiles/gdn_step_kernel_256_lanes.md); grows in proportion to lanes
 
 
 def peaks():
