@@ -35,6 +35,10 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
                 int n_split) {
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    // the norm weights do not depend on the predecessor: fetch them ahead of the wait, off the chain
+    uint4 wv[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) wv[c] = *reinterpret_cast<const uint4*>(w + c * 256 + lane * 8);
     pdl_wait();
     if (row >= rows) return;
     const uint16_t* src;
@@ -93,8 +97,7 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
         const int off = c * 256 + lane * 8;
-        const uint4 wv = *reinterpret_cast<const uint4*>(w + off);
-        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        const uint32_t ww[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -114,10 +117,11 @@ __global__ void __launch_bounds__(128)
 add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ parts, int n_split,
                       const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
                       uint16_t* __restrict__ normed_out, int rows) {
-    pdl_wait();
     __shared__ float red[4];
     const int row = blockIdx.x, tid = threadIdx.x;
     const int off = tid * 8;
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + off);      // ahead of the wait: weights are immutable
+    pdl_wait();
     const uint4 a = *reinterpret_cast<const uint4*>(x + (size_t)row * kHidden + off);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float* pp = parts + (size_t)row * kHidden + off;
@@ -172,7 +176,6 @@ add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ 
     if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
     const float inv = rsqrt_acc((red[0] + red[1] + red[2] + red[3]) * (1.0f / kHidden) + kEps);
-    const uint4 wv = *reinterpret_cast<const uint4*>(w + off);
     const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
     uint32_t o[4];
 #pragma unroll
@@ -186,6 +189,7 @@ cudaError_t launch_add_norm(const uint16_t* x, const int* ids, const uint16_t* t
                             const uint16_t* delta, const uint16_t* w, uint16_t* sum_out,
                             uint16_t* normed_out, int rows, cudaStream_t st, const float* delta_parts,
                             int n_split) {
+    if (w == nullptr) return cudaErrorInvalidValue;       // the kernels read the norm weights unconditionally
     if (delta_parts != nullptr && ids == nullptr && normed_out != nullptr)
         return launch_k(add_norm_split_kernel, dim3(rows), dim3(128), 0, st, x, delta_parts, n_split, w, sum_out,
                         normed_out, rows);
