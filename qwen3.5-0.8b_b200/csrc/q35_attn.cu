@@ -729,6 +729,280 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
     cluster_sync_all();                                    // (3) no CTA leaves while a peer may still read it
 }
 
+// ------------------------------------------------------------------------------------------------
+// Prompt bodies: causal attention of a block of 16 consecutive rows of one lane.
+// The row-by-row forms above read a lane's whole context once per row; a prompt body carries up to
+// 64 rows per lane, so here one CTA takes 16 rows x the 4 q heads of a kv head (64 q vectors) and
+// streams the K and V pages once per block: pass 1 over the K pages for the row maxima and sums
+// (kept per warp, combined once), pass 2 over (K, V) page pairs - scores recomputed bit for bit,
+// weights bf16(exp(s - M) / L) final before P.V, as in the one-row forms.  Scores come from
+// mma.sync with the q vectors as the B operand (bf16 hi + lo halves: f32-accurate q), the weights
+// go through shared memory to become the A operand of P.V.  Keys past a row's own position are
+// masked; pages past the block's last row are never fetched.  All rows of the body must already be
+// in the cache (attn_append_kernel).
+// ------------------------------------------------------------------------------------------------
+constexpr int kPfRows = 16;                   // rows (positions) per CTA
+constexpr int kPfQ = kPfRows * 4;             // q vectors per CTA; n = row * 4 + head
+constexpr int kPfQLd = 264;                   // bf16 row stride of a q tile (528 B: conflict-free ldmatrix)
+constexpr int kPfPLd = 72;                    // bf16 row stride of a weight tile (144 B)
+constexpr int kPfRing = 3;
+constexpr size_t kPfSmem = 1024 + (size_t)kPfRing * kTileBytes + 2 * (size_t)kPfQ * kPfQLd * 2 +
+                           2 * (size_t)kPfQ * kPfPLd * 2 + 4 * kPfQ * 2 * 4;
+
+__global__ void __launch_bounds__(kTmaThreads, 1)
+attn_prefill_kernel(AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * kPfRing];
+    pdl_wait();
+    if (p.status != nullptr && *p.status != 0) return;
+
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (ring - smem_u32(smem_raw));
+    uint16_t* Qhi = reinterpret_cast<uint16_t*>(base_ptr + kPfRing * kTileBytes);     // [64][264]
+    uint16_t* Qlo = Qhi + kPfQ * kPfQLd;
+    uint16_t* P_s = Qlo + kPfQ * kPfQLd;                                              // [2][64][72]
+    float* stat_s = reinterpret_cast<float*>(P_s + 2 * kPfQ * kPfPLd);                // [4 m-tiles][64][2]
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kPfRing]);
+
+    const int lane_id = blockIdx.x, kvh = blockIdx.y, t0 = blockIdx.z * kPfRows;
+    const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    const int g = ln >> 2, t = ln & 3;
+    const int cap = p.pages_per_lane * kKvPage;
+    const int slot0 = p.slot[lane_id];                      // position of the body's first row
+    const int rope0 = p.rope_pos[lane_id];
+    const int rows_here = (p.T - t0) < kPfRows ? (p.T - t0) : kPfRows;
+    int last = slot0 + t0 + rows_here - 1;                  // last key position any row of the block sees
+    if (last >= cap) last = cap - 1;
+    const int P = last / kKvPage + 1;                       // pages the block reads
+    const int* table = p.page_table + (size_t)lane_id * p.table_lane_stride;
+
+    if (tid == 0) {
+        for (int b = 0; b < kPfRing; ++b) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(full0 + 8 * b) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;\n" ::"r"(empty0 + 8 * b) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 8) {
+        // ---- producer: K pages 0..P-1, then (K, V) of page 0, of page 1, ... ---------------------
+        if (ln == 0) {
+            bool ok = true;
+            for (int i = 0; i < 3 * P && ok; ++i) {
+                const int b = i % kPfRing;
+                ok = mbar_wait(empty0 + 8 * b, ((i / kPfRing) & 1) ^ 1);
+                if (!ok) break;
+                const int page_i = i < P ? i : ((i - P) >> 1);
+                const bool is_v = i >= P && ((i - P) & 1);
+                const CUtensorMap* map = is_v ? &vmap : &kmap;
+                const uint32_t dst = ring + b * kTileBytes;
+                const int r0 = table[page_i] * (kKvHeads * kKvPage) + kvh * kKvPage;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(full0 + 8 * b), "r"(kTileBytes) : "memory");
+#pragma unroll
+                for (int cb = 0; cb < 4; ++cb)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                        ::"r"(dst + cb * 8192), "l"(reinterpret_cast<uint64_t>(map)), "r"(full0 + 8 * b), "r"(cb * 64), "r"(r0) : "memory");
+            }
+            if (!ok && p.status != nullptr) atomicExch(p.status, 5);
+        }
+        return;
+    }
+
+    // ---- q vectors of the block: norm + rope in f32, split into bf16 hi + lo ----------------------
+    for (int n = warp * 8; n < warp * 8 + 8; ++n) {
+        const int r = n >> 2, head = kvh * 4 + (n & 3);
+        uint4 hi4 = make_uint4(0, 0, 0, 0), lo4 = make_uint4(0, 0, 0, 0);
+        if (r < rows_here) {                                   // warp-uniform
+            const uint16_t* pr = p.proj + ((size_t)lane_id * p.T + t0 + r) * kAttnProjN;
+            float x[8], h8[8], l8[8];
+            unpack8(*reinterpret_cast<const uint4*>(pr + head * 2 * kHeadDim + 8 * ln), x);
+            head_norm_rope(x, p.q_norm, ln, rope0 + t0 + r, p.inv_freq);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { h8[e] = bfround(x[e]); l8[e] = x[e] - h8[e]; }
+            hi4 = pack8(h8);
+            lo4 = pack8(l8);
+        }
+        *reinterpret_cast<uint4*>(Qhi + n * kPfQLd + 8 * ln) = hi4;
+        *reinterpret_cast<uint4*>(Qlo + n * kPfQLd + 8 * ln) = lo4;
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+
+    const int mt = warp & 3, nh = warp >> 2;               // 16-position m-tile, 32-q-vector half
+    bool ok = true;
+    // scores of this warp's (m-tile, q half) for the page in ring slot `tile`: acc[nt][0..3]
+    auto scores = [&](uint32_t tile, float (&acc)[4][4]) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+#pragma unroll 4
+        for (int ks = 0; ks < 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(a, tile + tile_off(mt * 16 + (ln & 15), ks * 2 + (ln >> 4)));
+            const int blk = ln >> 3, rr = ln & 7;
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                const int n = nh * 32 + (np * 2 + (blk >> 1)) * 8 + rr;
+                const uint32_t off = (uint32_t)(n * kPfQLd + ks * 16 + (blk & 1) * 8) * 2;
+                uint32_t bh[4], bl[4];
+                ldsm_x4(bh, smem_u32(Qhi) + off);
+                ldsm_x4(bl, smem_u32(Qlo) + off);
+                mma_bf16(acc[2 * np], a[0], a[1], a[2], a[3], bh[0], bh[1]);
+                mma_bf16(acc[2 * np], a[0], a[1], a[2], a[3], bl[0], bl[1]);
+                mma_bf16(acc[2 * np + 1], a[0], a[1], a[2], a[3], bh[2], bh[3]);
+                mma_bf16(acc[2 * np + 1], a[0], a[1], a[2], a[3], bl[2], bl[3]);
+            }
+        }
+    };
+    // key position limit of the q vector in column (nt, e & 1): its own row's position; -1 = no row
+    auto limit_of = [&](int nt, int e) {
+        const int n = nh * 32 + nt * 8 + 2 * t + (e & 1);
+        const int r = n >> 2;
+        return r < rows_here ? slot0 + t0 + r : -1;
+    };
+
+    // ---- pass 1: per-column running max and sum over this warp's positions ------------------------
+    float M[8], L[8];
+#pragma unroll
+    for (int c8 = 0; c8 < 8; ++c8) { M[c8] = -INFINITY; L[c8] = 0.f; }
+    for (int j = 0; j < P; ++j) {
+        const int b = j % kPfRing;
+        if (ok) ok = mbar_wait(full0 + 8 * b, (j / kPfRing) & 1);
+        float acc[4][4];
+        scores(ring + b * kTileBytes, acc);
+        __syncwarp();
+        if (ln == 0) mbar_arrive(empty0 + 8 * b);
+        const int pos_lo = j * kKvPage + mt * 16 + g;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int lim = limit_of(nt, e);
+                const float s0 = pos_lo <= lim ? acc[nt][e] * 0.0625f : -INFINITY;
+                const float s1 = pos_lo + 8 <= lim ? acc[nt][2 + e] * 0.0625f : -INFINITY;
+                float pm = fmaxf(s0, s1);
+                pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 4));
+                pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 8));
+                pm = fmaxf(pm, __shfl_xor_sync(0xffffffffu, pm, 16));
+                const int c8 = nt * 2 + e;
+                const float Mn = fmaxf(M[c8], pm);
+                float add = 0.f;
+                if (Mn > -INFINITY) add = (s0 > -INFINITY ? expf(s0 - Mn) : 0.f) + (s1 > -INFINITY ? expf(s1 - Mn) : 0.f);
+                add += __shfl_xor_sync(0xffffffffu, add, 4);
+                add += __shfl_xor_sync(0xffffffffu, add, 8);
+                add += __shfl_xor_sync(0xffffffffu, add, 16);
+                if (Mn > -INFINITY) L[c8] = L[c8] * (M[c8] > -INFINITY ? expf(M[c8] - Mn) : 0.f) + add;
+                M[c8] = Mn;
+            }
+    }
+    if (g == 0) {
+#pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+            const int n = nh * 32 + (c8 >> 1) * 8 + 2 * t + (c8 & 1);
+            stat_s[(mt * kPfQ + n) * 2] = M[c8];
+            stat_s[(mt * kPfQ + n) * 2 + 1] = L[c8];
+        }
+    }
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
+#pragma unroll
+    for (int c8 = 0; c8 < 8; ++c8) {
+        const int n = nh * 32 + (c8 >> 1) * 8 + 2 * t + (c8 & 1);
+        float Mf = -INFINITY;
+#pragma unroll
+        for (int m4 = 0; m4 < 4; ++m4) Mf = fmaxf(Mf, stat_s[(m4 * kPfQ + n) * 2]);
+        float Lf = 0.f;
+#pragma unroll
+        for (int m4 = 0; m4 < 4; ++m4) {
+            const float mm = stat_s[(m4 * kPfQ + n) * 2], ll = stat_s[(m4 * kPfQ + n) * 2 + 1];
+            if (ll > 0.f) Lf += ll * expf(mm - Mf);
+        }
+        M[c8] = Mf;
+        L[c8] = Lf;
+    }
+
+    // ---- pass 2: weights of a page -> shared memory -> P.V ---------------------------------------
+    float O[4][4][4];
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) O[mm][nt][e] = 0.f;
+    for (int j = 0; j < P; ++j) {
+        const int ik = P + 2 * j, iv = ik + 1;
+        const int bk = ik % kPfRing, bv = iv % kPfRing;
+        if (ok) ok = mbar_wait(full0 + 8 * bk, (ik / kPfRing) & 1);
+        float acc[4][4];
+        scores(ring + bk * kTileBytes, acc);
+        __syncwarp();
+        if (ln == 0) mbar_arrive(empty0 + 8 * bk);
+        uint16_t* Pw = P_s + (j & 1) * kPfQ * kPfPLd;
+        const int pos_lo = j * kKvPage + mt * 16 + g;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int lim = limit_of(nt, e);
+                const int c8 = nt * 2 + e;
+                const int n = nh * 32 + nt * 8 + 2 * t + e;
+                const float w0 = pos_lo <= lim ? __fdiv_rn(expf(acc[nt][e] * 0.0625f - M[c8]), L[c8]) : 0.f;
+                const float w1 = pos_lo + 8 <= lim ? __fdiv_rn(expf(acc[nt][2 + e] * 0.0625f - M[c8]), L[c8]) : 0.f;
+                Pw[n * kPfPLd + mt * 16 + g] = f2bf(w0);
+                Pw[n * kPfPLd + mt * 16 + g + 8] = f2bf(w1);
+            }
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (ok) ok = mbar_wait(full0 + 8 * bv, (iv / kPfRing) & 1);
+        const uint32_t vt = ring + bv * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            uint32_t bfr[2][4];
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                const int pos = ks * 16 + (ln & 7) + ((ln >> 3) & 1) * 8;
+                ldsm_x4_trans(bfr[np], vt + tile_off(pos, warp * 4 + np * 2 + (ln >> 4)));
+            }
+#pragma unroll
+            for (int mm = 0; mm < 4; ++mm) {
+                uint32_t a[4];
+                ldsm_x4(a, smem_u32(Pw) + (uint32_t)((mm * 16 + (ln & 15)) * kPfPLd + ks * 16 + (ln >> 4) * 8) * 2);
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    mma_bf16(O[mm][2 * np], a[0], a[1], a[2], a[3], bfr[np][0], bfr[np][1]);
+                    mma_bf16(O[mm][2 * np + 1], a[0], a[1], a[2], a[3], bfr[np][2], bfr[np][3]);
+                }
+            }
+        }
+        __syncwarp();
+        if (ln == 0) mbar_arrive(empty0 + 8 * bv);
+    }
+    if (!ok) {
+        if (ln == 0 && p.status != nullptr) atomicExch(p.status, 6);
+        return;
+    }
+
+    // ---- epilogue: round, apply the bf16 sigmoid gate ---------------------------------------------
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm)
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int n = mm * 16 + g + hrow * 8;
+            const int r = n >> 2, head = kvh * 4 + (n & 3);
+            if (r >= rows_here) continue;
+            const size_t row = (size_t)lane_id * p.T + t0 + r;
+            const uint16_t* pr = p.proj + row * kAttnProjN;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int dd = warp * 32 + nt * 8 + 2 * t;
+                const uint32_t gw = *reinterpret_cast<const uint32_t*>(pr + head * 2 * kHeadDim + kHeadDim + dd);
+                const float o0 = bfround(O[mm][nt][2 * hrow]) * bfround(sigmoid_acc(lo_bf(gw)));
+                const float o1 = bfround(O[mm][nt][2 * hrow + 1]) * bfround(sigmoid_acc(hi_bf(gw)));
+                *reinterpret_cast<uint32_t*>(p.out + row * (kQHeads * kHeadDim) + head * kHeadDim + dd) = pack_bf2(o0, o1);
+            }
+        }
+}
+
 size_t attn_tma_smem(int ctx_pad) {
     return 1024 + (size_t)kRing * kTileBytes + 4 * kHeadDim * 4 + (size_t)8 * ctx_pad * 4 + (size_t)4 * ctx_pad * 2;
 }
@@ -777,6 +1051,8 @@ cudaError_t attn_init() {
     const int tma_bytes = (int)attn_tma_smem(kAttnTmaMaxCtx);
     e = cudaFuncSetAttribute(attn_tma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPfSmem);
+    if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(attn_cluster_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
     if (e != cudaSuccess) return e;
     e = cudaFuncSetAttribute(attn_cluster_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, tma_bytes);
@@ -792,6 +1068,23 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
     if (p.T > 1) {
         cudaError_t e = launch_k(attn_append_kernel, grid, dim3(64), 0, st, p);
         if (e != cudaSuccess) return e;
+    }
+    // prompt bodies: blocks of 16 rows share one pass over the lane's pages
+    static int prefill_mode = -1;
+    if (prefill_mode < 0) {
+        const char* env = std::getenv("Q35_ATTN_PREFILL");
+        prefill_mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    if (prefill_mode && p.T >= kPfRows) {
+        CUtensorMap kmap, vmap;
+        if (p.kmap != nullptr && p.vmap != nullptr) {
+            kmap = *static_cast<const CUtensorMap*>(p.kmap);
+            vmap = *static_cast<const CUtensorMap*>(p.vmap);
+        } else if (!attn_make_pool_map(&kmap, p.kpool, p.n_pages) || !attn_make_pool_map(&vmap, p.vpool, p.n_pages)) {
+            return cudaErrorInvalidValue;
+        }
+        return launch_k(attn_prefill_kernel, dim3(p.lanes, kKvHeads, (p.T + kPfRows - 1) / kPfRows), dim3(kTmaThreads),
+                        kPfSmem, st, p, kmap, vmap);
     }
     if (ctx_pad <= kAttnTmaMaxCtx) {
         CUtensorMap kmap, vmap;

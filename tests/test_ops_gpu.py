@@ -340,6 +340,52 @@ def test_attn_decode_vs_oracle(eng, weights, ctxs):
         assert torch.equal(vd[pg, :, c % 64], refs[i][2])
 
 
+@pytest.mark.parametrize("ctxs,T", [([0, 0], 64), ([10, 100], 16), ([0, 37, 64, 500], 40), ([200], 17), ([960], 64)])
+def test_attn_prompt_body_vs_oracle(eng, weights, ctxs, T):
+    """A prompt body of T >= 16 rows per lane on top of ragged cached contexts: the block-of-16-rows
+    causal kernel against the oracle's batched causal attention (f32 softmax over each row's own
+    prefix), row by row, plus the appended keys / values."""
+    l = 11
+    pre = f"{O.LM}layers.{l}.self_attn."
+    lanes = len(ctxs)
+    gen = torch.Generator().manual_seed(sum(ctxs) + T)
+    Ks, Vs, projs, refs, newk, newv = [], [], [], [], [], []
+    for c in ctxs:
+        kv = {}
+        if c > 0:
+            O.attn_mixer(weights, pre, torch.randn((c, 1024), generator=gen).to(torch.bfloat16), 0, kv, True)
+        Ks.append(torch.cat(kv["k"], 0) if c else torch.zeros((0, 2, 256)))
+        Vs.append(torch.cat(kv["v"], 0) if c else torch.zeros((0, 2, 256), dtype=torch.bfloat16))
+        h = torch.randn((T, 1024), generator=gen).to(torch.bfloat16)
+        d = {}
+        O.attn_mixer(weights, pre, h, c, kv, True, d)
+        refs.append(d["gated"])
+        newk.append(torch.cat(kv["k"], 0)[c:])
+        newv.append(torch.cat(kv["v"], 0)[c:])
+        projs.append(torch.cat([d["qg"].reshape(T, -1), d["k_raw"].reshape(T, -1), d["v_raw"].reshape(T, -1)], -1))
+    ppl = (max(ctxs) + T) // 64 + 1
+    kpool, vpool, table = paged(Ks, Vs, ppl, lanes)
+    kd, vd = cu(kpool), cu(vpool)
+    out = eng.op_attn_decode(cu(torch.cat(projs, 0)), cu(weights[pre + "q_norm.weight"]),
+                             cu(weights[pre + "k_norm.weight"]), kd, vd, cu(table),
+                             cu(torch.tensor(ctxs, dtype=torch.int32)), lanes, T=T).cpu()
+    kd, vd = kd.cpu(), vd.cpu()
+    worst = 0.0
+    for i, c in enumerate(ctxs):
+        o = out[i * T:(i + 1) * T].float()
+        ref = refs[i].float().reshape(T, -1)
+        for r in range(T):
+            e = rel_l2(o[r], ref[r])
+            worst = max(worst, e)
+            assert e <= 1e-2, (c, r, e)
+        for r in (0, T // 2, T - 1):
+            pos = c + r
+            pg = int(table[i, pos // 64])
+            assert rel_l2(kd[pg, :, pos % 64].float(), newk[i][r]) < 2e-3
+            assert torch.equal(vd[pg, :, pos % 64], newv[i][r])
+    note(f"attn_prompt_body_T{T}_lanes{lanes}_worst_rel_l2", worst)
+
+
 def test_attn_long_context_form(eng, weights):
     """Contexts beyond 1,024 positions (the plain-load kernel; up to the 8,192-position cap) on
     synthetic caches (keys N(0, 0.25), values N(0, 1): thousands of positions carry weight)."""
