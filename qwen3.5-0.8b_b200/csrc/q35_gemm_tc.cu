@@ -16,6 +16,7 @@
 // skips its stores, still frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <cmath>
 #include <cstdlib>
 
 #include "q35_common.cuh"
@@ -592,6 +593,10 @@ int linear_tc_splits(int rows, int N, int K, int max_rows_ws) {
     int splits = (148 + tiles - 1) / tiles;
     if (splits > num_kb / 4) splits = num_kb / 4;        // at least 4 k-blocks per split
     if (splits > kMaxSplits) splits = kMaxSplits;
+    // Every split writes and the add + norm kernel reads a rows x N f32 partial: the best split count
+    // falls with the row count (measured: 8 at 128 rows, 6 at 256, 4 at 512), about 90 / sqrt(rows).
+    const int by_rows = (int)lroundf(90.5f / sqrtf((float)rows));
+    if (splits > by_rows) splits = by_rows;
     if (splits < 2) return 1;
     const int kb_per = (num_kb + splits - 1) / splits;
     return (num_kb + kb_per - 1) / kb_per;               // every split gets at least one k-block
