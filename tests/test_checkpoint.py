@@ -41,6 +41,22 @@ def test_normalize_name_rules(ck):
         assert ck.normalize_name(ck.denormalize_name(n)) == (ck.LOAD, n)
 
 
+def test_text_path_tables_match_the_reference_counts(ck):
+    """The reference's load gate G0 (speccheck/specimpl.py:61-63): 335 of the shard's 488 tensors are
+    the text path (153 vision tensors skipped); exactly 36 of them are F32 (A_log and the gated-norm
+    weight of the 18 GatedDeltaNet layers, specification/01-weights-and-shapes.md section 01.6)."""
+    spec = ck.expected_spec(None, None, True)
+    assert len(spec) == 335
+    f32 = [n for n, (dt, _) in spec.items() if dt == "F32"]
+    assert len(f32) == 36 and all(n.endswith(ck.F32_SUFFIXES) for n in f32)
+    assert spec["model.language_model.embed_tokens.weight"] == ("BF16", (248320, 1024))
+    assert spec["mtp.fc.weight"] == ("BF16", (1024, 2048))
+    assert spec["model.language_model.layers.0.linear_attn.conv1d.weight"] == ("BF16", (6144, 1, 4))
+    assert len([n for n in spec if n.startswith("mtp.")]) == 15
+    nbytes = sum((4 if dt == "F32" else 2) * __import__("math").prod(shape) for dt, shape in spec.values())
+    assert abs(nbytes / 1e9 - 1.5457) < 5e-4          # the text-only total of section 01.7
+
+
 def test_round_trip_verified(ck, params, tmp_path):
     ck.save_checkpoint(params, tmp_path, n_vision_dummies=7)
     store, stats = load(ck, tmp_path, verify=True)
