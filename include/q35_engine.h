@@ -113,7 +113,8 @@ typedef struct {
     long long kv_bytes_per_pos;   /* 12,288                                                 */
     long long flops_per_row;      /* matmul flops per token                                 */
     int launches_decode;          /* kernels one q35_decode_step enqueues (more than 16 lanes) */
-    int launches_decode_few_lanes;/* the same at <= 16 lanes: one persistent kernel                  */
+    int launches_decode_few_lanes;/* the same at <= 16 lanes: equal to launches_decode unless the
+                                     one-kernel step was switched on (Q35_SMALL_STEP=1)              */
 } q35_census;
 
 const char* q35_last_error(void);

@@ -266,6 +266,7 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
                 const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
+    if (threadIdx.x == 0) { prefetch_tensormap(&kmap); prefetch_tensormap(&vmap); }
     pdl_wait();
     if (p.status != nullptr && *p.status != 0) return;
 
@@ -494,6 +495,7 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
                     const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
+    if (threadIdx.x == 0) { prefetch_tensormap(&kmap); prefetch_tensormap(&vmap); }
     __shared__ float ml_s[8];                              // local max [4 heads] | local sum of exp [4]
     __shared__ float ML_s[8];                              // the row's max | 1 / sum
     __shared__ __align__(16) float o_part[4 * kHeadDim];   // this CTA's f32 partial of P.V
@@ -753,6 +755,7 @@ __global__ void __launch_bounds__(kTmaThreads, 1)
 attn_prefill_kernel(AttnParams p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kPfRing];
+    if (threadIdx.x == 0) { prefetch_tensormap(&kmap); prefetch_tensormap(&vmap); }
     pdl_wait();
     if (p.status != nullptr && *p.status != 0) return;
 

@@ -85,7 +85,8 @@ __device__ __forceinline__ void head_norm_rope(float (&x)[8], const uint16_t* __
         if (ln < 8) {
             const int i = (8 * ln + e) & 31;
             const float ang = __fmul_rn((float)rope_pos, inv_freq[i]);
-            const float c = cosf(ang), s = sinf(ang);
+            float s, c;
+            sincosf(ang, &s, &c);                 // one argument reduction for both
             const float sw = ln < 4 ? -partner : partner;
             x[e] = __fadd_rn(__fmul_rn(x[e], c), __fmul_rn(sw, s));
         }
@@ -116,6 +117,12 @@ __device__ __forceinline__ bool better(float av, int ai, float bv, int bi) {
 // beside its predecessor and everything older than the predecessor is complete.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// The TMA unit fetches a tensor map (128 bytes of kernel parameter space) on first use; asking for
+// it at kernel entry takes that fetch off the first tile's critical path.
+__device__ __forceinline__ void prefetch_tensormap(const void* map) {
+    asm volatile("prefetch.tensormap [%0];\n" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 
 bool pdl_enabled();            // Q35_PDL=1/0 forces; unset: on for bodies of few rows (pdl_set_rows)
 void pdl_set_rows(int rows);   // the engine announces the row count of the body it is about to launch

@@ -198,6 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant_
     __shared__ int abort_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) { prefetch_tensormap(&tma_w); prefetch_tensormap(&tma_x); }
     const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     // K split: this CTA covers k-blocks [kb0, kb0 + num_kb)
     const int kb_per = (num_kb_total + gridDim.z - 1) / gridDim.z;
@@ -346,6 +347,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_c
     __shared__ int issued_s, consumed_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) { prefetch_tensormap(&tma_w); prefetch_tensormap(&tma_x); }
     const int total = m_tiles * n_tiles;
     const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
