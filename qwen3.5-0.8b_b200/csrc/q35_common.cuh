@@ -66,25 +66,34 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 
 // Zero-centred RMSNorm of one 256-wide head held 8 values per lane, then partial RoPE.
 // Returns the f32 result in x (rotated dims are NOT rounded; un-rotated dims are bf16 values).
+// The norm weights and the lane's eight rotation frequencies are requested first, so their latency
+// overlaps the reduction instead of following it.
 __device__ __forceinline__ void head_norm_rope(float (&x)[8], const uint16_t* __restrict__ w, int ln,
                                                int rope_pos, const float* __restrict__ inv_freq) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + 8 * ln);
+    // lanes 0..3 hold dims 0..31, lanes 4..7 hold dims 32..63; dim d rotates with frequency d & 31
+    float4 f0 = make_float4(0.f, 0.f, 0.f, 0.f), f1 = f0;
+    if (ln < 8) {
+        const float4* fp = reinterpret_cast<const float4*>(inv_freq + ((8 * ln) & 31));
+        f0 = fp[0];
+        f1 = fp[1];
+    }
     float ss = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += x[e] * x[e];
     ss = warp_sum(ss);
     const float inv = rsqrt_acc(ss * (1.0f / kHeadDimC) + kEps);
-    const uint4 wv = *reinterpret_cast<const uint4*>(w + 8 * ln);
     float wf[8];
     unpack8(wv, wf);
 #pragma unroll
     for (int e = 0; e < 8; ++e) x[e] = bfround(__fmul_rn(__fmul_rn(x[e], inv), 1.0f + wf[e]));
-    // lanes 0..3 hold dims 0..31, lanes 4..7 hold dims 32..63; partner of dim d is d ^ 32
+    const float fr[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+    // the partner of dim d is d ^ 32: four lanes away
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         const float partner = __shfl_xor_sync(0xffffffffu, x[e], 4);
         if (ln < 8) {
-            const int i = (8 * ln + e) & 31;
-            const float ang = __fmul_rn((float)rope_pos, inv_freq[i]);
+            const float ang = __fmul_rn((float)rope_pos, fr[e]);
             float s, c;
             sincosf(ang, &s, &c);                 // one argument reduction for both
             const float sw = ln < 4 ? -partner : partner;
