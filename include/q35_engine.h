@@ -158,6 +158,9 @@ int q35_state_positions(q35_state* s, int* positions_out, void* stream);
  * (RequestState::check_invariants, engine/state.h:99).  A caller that replays a captured CUDA graph
  * of the step reports the replayed steps here; the captured call itself already counted once. */
 int q35_state_note_advance(q35_state* s, int n);
+/* Speculative rounds advance a lane by 1..k+1 positions on the device; the host's bound moves by the
+ * maximum.  This reads the true positions back (stream synchronisation) and tightens the bound. */
+int q35_state_sync_bound(q35_state* s, void* stream);
 /* Copy one lane's tuple out of / into the reference layouts (engine/state.h:86-92):
  * gdn_state f32 [18][16][128][128] (S[i][j], i over d_k), conv_window f32 [18][3][6144] row 0
  * oldest, kv_keys / kv_values bf16 [6][2][cap][256].  Null pointers are skipped. */
@@ -188,6 +191,9 @@ int q35_prefill(q35_engine* e, q35_state* s, const int* ids, int T, int* y0,
 int q35_mtp_state_create(q35_engine* e, q35_state* s, int max_ctx, q35_mtp_state** out);
 int q35_mtp_state_destroy(q35_mtp_state* m);
 int q35_mtp_state_reset(q35_mtp_state* m, void* stream);
+/* The draft cache's host bound only grows (one row per draft), while a round that does not accept
+ * everything drops its rows on the device: read the true lengths back and tighten the bound. */
+int q35_mtp_state_sync_bound(q35_mtp_state* m, void* stream);
 /* Replaces mtpdraft::draft_round (engine/mtp_draft.h:233): from the target's post-final-norm rows
  * h_norm [lanes][1024], the just-emitted tokens y_next [lanes] and the drafted positions
  * pos [lanes], propose proposal [lanes] and append one row to each lane's draft cache. */

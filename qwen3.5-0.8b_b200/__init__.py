@@ -6,4 +6,5 @@ from . import engine  # noqa: F401
 from . import parallel  # noqa: F401
 from . import checkpoint  # noqa: F401
 from . import session  # noqa: F401
+from . import mtp_adaptive  # noqa: F401
 from .engine import Engine, LaneState, MtpState, Q35Error, StepGraph, load_library  # noqa: F401

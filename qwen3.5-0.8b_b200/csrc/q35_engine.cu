@@ -557,6 +557,21 @@ extern "C" int q35_state_note_advance(q35_state* s, int n) {
     return Q35_OK;
 }
 
+// Speculative rounds advance a lane by 1..k+1 positions and the host cannot know by how many without
+// reading back, so its bound moves by the maximum every round.  This call reads the true positions
+// (one small copy and a stream synchronisation) and tightens the bound to their maximum.
+extern "C" int q35_state_sync_bound(q35_state* s, void* stream) {
+    REQUIRE(s, Q35_ERR_ARG, "q35_state_sync_bound: null state");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    std::vector<int> pos(s->lanes);
+    CK(cudaMemcpyAsync(pos.data(), s->pos, s->lanes * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    int hi = 0;
+    for (int v : pos) hi = v > hi ? v : hi;
+    s->host_pos_hi = hi;
+    return Q35_OK;
+}
+
 static int host_sel(q35_state* s, int lane, cudaStream_t st, int* out) {
     *out = 0;
     if (s->sel) {
@@ -780,6 +795,20 @@ extern "C" int q35_mtp_state_reset(q35_mtp_state* m, void* stream) {
     REQUIRE(m, Q35_ERR_ARG, "q35_mtp_state_reset: null state");
     CK(cudaMemsetAsync(m->n, 0, m->lanes * sizeof(int), static_cast<cudaStream_t>(stream)));
     m->host_n_hi = 0;
+    return Q35_OK;
+}
+
+// The same for the draft cache: a round that does not accept everything drops its k rows on the
+// device, while the host's bound only ever grows.
+extern "C" int q35_mtp_state_sync_bound(q35_mtp_state* m, void* stream) {
+    REQUIRE(m, Q35_ERR_ARG, "q35_mtp_state_sync_bound: null state");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    std::vector<int> n(m->lanes);
+    CK(cudaMemcpyAsync(n.data(), m->n, m->lanes * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    int hi = 0;
+    for (int v : n) hi = v > hi ? v : hi;
+    m->host_n_hi = hi;
     return Q35_OK;
 }
 

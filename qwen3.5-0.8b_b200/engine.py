@@ -64,7 +64,8 @@ EXPORTS = [
     "q35_state_positions", "q35_state_note_advance", "q35_state_export_lane", "q35_state_import_lane",
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
     "q35_mtp_state_reset", "q35_mtp_draft", "q35_mtp_verify", "q35_mtp_state_reserve_depth",
-    "q35_mtp_draft_k", "q35_mtp_verify_k", "q35_op_add_norm", "q35_op_linear",
+    "q35_mtp_draft_k", "q35_mtp_verify_k", "q35_state_sync_bound", "q35_mtp_state_sync_bound",
+    "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
     "q35_lm_head_argmax_static",
 ]
@@ -154,6 +155,10 @@ class LaneState:
     def note_advance(self, n: int):
         _check(self.engine.lib.q35_state_note_advance(self.handle, n))
 
+    def sync_bound(self):
+        """Tighten the host's position bound to the lanes' true maximum (synchronises the stream)."""
+        _check(self.engine.lib.q35_state_sync_bound(self.handle, _stream()))
+
     @staticmethod
     def sizes(lanes: int, max_ctx: int) -> dict:
         s = StateSizes()
@@ -200,6 +205,10 @@ class MtpState:
 
     def reset(self):
         _check(self.engine.lib.q35_mtp_state_reset(self.handle, _stream()))
+
+    def sync_bound(self):
+        """Tighten the host's draft-cache length bound to the true maximum (synchronises the stream)."""
+        _check(self.engine.lib.q35_mtp_state_sync_bound(self.handle, _stream()))
 
     def close(self):
         if self.handle:
