@@ -4,7 +4,8 @@
 // Persistent CTAs (two per SM; each keeps one head and strides over lanes) walk the (lane, head)
 // items of a layer.  Everything the NEXT item needs from HBM - its 64 KiB head state, its q/k/v
 // rows, conv window rows and z row - is fetched into shared memory by bulk async copies
-// (cp.async.bulk, completion on one mbarrier) while the current item is updated, so every SM keeps
+// (one cp.async.bulk for the tile, one 3-D and one 4-D tensor copy for the small pieces, completion
+// on one mbarrier) while the current item is updated, so every SM keeps
 // state loads in flight all the time and no global-load latency sits on an item's critical path.
 // The current tile lives in registers (thread = 16 rows x 4 columns): both reductions of the
 // update (r = S^T k and o = S^T q) run on the register copy with a cross-warp shared-memory reduce,
@@ -18,7 +19,10 @@
 //
 // Replaces gdn_conv / gdn_gates / gdn_rec / gdn_gated_norm (engine/kernels.h:398-460,682);
 // arithmetic follows speccheck/specimpl.py:252-305 as executed.
+#include <cuda.h>
+
 #include <cstdlib>
+#include <unordered_map>
 
 #include "q35_common.cuh"
 
@@ -61,34 +65,31 @@ constexpr uint32_t kInBytes = kInRows * 128 * sizeof(uint16_t);
 constexpr uint32_t kFetchBytes = kTileBytes + kInBytes;
 constexpr size_t kGdnSmemBytes = kTileBytes + kInBytes;
 
-// Everything item (lane_id, h) needs from HBM for its first token, as bulk copies that complete on
-// one mbarrier: the 64 KiB state tile and thirteen 256-byte rows of small inputs.  The fourteen
-// copies are issued by fourteen lanes of one warp at once (`part` = lane): 0 = expect_tx + tile,
-// 1..3 = raw q, k, v rows, 4..12 = window rows, 13 = z row.  `what` bit 0: the state tile and conv
-// window (written by this layer's previous step only), bit 1: the rows of this step's projection;
-// the first may be issued before the projection kernel ahead of this one has ended.
-// Every lane of the warp must call this (it contains a warp barrier).
-__device__ __forceinline__ void item_fetch_part(const GdnParams& p, int lane_id, int h, int part, int what,
-                                                uint32_t tile_addr, uint32_t in_addr, uint32_t bar) {
+// Everything item (lane_id, h) needs from HBM for its first token, as THREE copies that complete on
+// one mbarrier (issuing a copy costs the issuing warp ~130 cycles, one after the other, on the chain
+// every warp waits for): the 64 KiB state tile (bulk copy), the head's q | k | v | z pieces of the
+// projection row (one 3-D tensor copy: 4 pieces of 128 values, 2048 apart), and the head's 3 x 3
+// conv-window pieces (one 4-D tensor copy).  Shared-memory rows: 0..3 = q, k, v, z; 4 + 3 j + kind =
+// window row j of kind.  `what` bit 0: the state tile and conv window (written by this layer's
+// previous step only), bit 1: the projection pieces; the first may be issued before the projection
+// kernel ahead of this one has ended.
+__device__ __forceinline__ void item_fetch(const GdnParams& p, const CUtensorMap* pmap, const CUtensorMap* wmap0,
+                                           const CUtensorMap* wmap1, const CUtensorMap* wmap2, int lane_id, int h,
+                                           int what, uint32_t tile_addr, uint32_t in_addr, uint32_t bar) {
     const int sel = p.sel != nullptr ? p.sel[lane_id] : 0;
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     if (what & 1) {
-        if (part == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
-            bulk_g2s(tile_addr, pick_buf(p.S, sel) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv), kTileBytes, bar);
-        }
-        __syncwarp();                      // the transaction count is armed before any other copy can land
-        if (part >= 4 && part <= 12) {
-            const int j = (part - 4) / 3, kind = (part - 4) % 3;
-            const uint16_t* win = pick_buf(p.win, sel) + (size_t)lane_id * 3 * kConvCh;
-            bulk_g2s(in_addr + (3 + j * 3 + kind) * 256, win + j * kConvCh + kind * 2048 + h * 128, 256, bar);
-        }
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(kFetchBytes) : "memory");
+        bulk_g2s(tile_addr, pick_buf(p.S, sel) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv), kTileBytes, bar);
+        const CUtensorMap* wm = sel == 0 ? wmap0 : (sel == 1 ? wmap1 : wmap2);
+        asm volatile(
+            "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];\n"
+            ::"r"(in_addr + 4 * 256), "l"(reinterpret_cast<uint64_t>(wm)), "r"(bar), "r"(h * 128), "r"(0), "r"(0), "r"(lane_id) : "memory");
     }
-    if (what & 2) {
-        const uint16_t* pr = p.proj + (size_t)lane_id * p.T * kGdnProjN;
-        if (part >= 1 && part <= 3) bulk_g2s(in_addr + (part - 1) * 256, pr + (part - 1) * 2048 + h * 128, 256, bar);
-        if (part == 13) bulk_g2s(in_addr + 12 * 256, pr + kOffZ + h * 128, 256, bar);
-    }
+    if (what & 2)
+        asm volatile(
+            "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+            ::"r"(in_addr), "l"(reinterpret_cast<uint64_t>(pmap)), "r"(bar), "r"(h * 128), "r"(0), "r"(lane_id * p.T) : "memory");
 }
 
 // conv taps stay packed as two bf16 pairs; f32 taps in ascending order, one bf16 rounding, SiLU in bf16
@@ -107,7 +108,9 @@ __device__ __forceinline__ float conv_silu(float (&w)[3], float raw, uint2 tap) 
 // copied to registers, in the shadow of that item's conv (which warps 0-3 carry the longer half
 // of), so neither the norm nor the fetch sits on the chain conv -> pass 1 -> pass 2 -> stores that
 // every warp walks.
-__global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
+__global__ void __launch_bounds__(256, 2)
+gdn_step_kernel(GdnParams p, const __grid_constant__ CUtensorMap pmap, const __grid_constant__ CUtensorMap wmap0,
+                const __grid_constant__ CUtensorMap wmap1, const __grid_constant__ CUtensorMap wmap2) {
     extern __shared__ __align__(128) unsigned char dyn_smem[];
     float* tile = reinterpret_cast<float*>(dyn_smem);                          // 128x128 f32 head tile
     uint16_t* in_s = reinterpret_cast<uint16_t*>(dyn_smem + kTileBytes);       // [13][128] bf16
@@ -136,11 +139,11 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
         }
         __syncthreads();
         // the first state tile is on its way before the projection kernel ahead of this one has ended
-        if (issuer && l0 < p.lanes) item_fetch_part(p, l0, h, ln, 1, tile_addr, in_addr, bar);
+        if (tid == 128 && l0 < p.lanes) item_fetch(p, &pmap, &wmap0, &wmap1, &wmap2, l0, h, 1, tile_addr, in_addr, bar);
         pdl_wait();
         if (issuer && l0 < p.lanes) {
-            item_fetch_part(p, l0, h, ln, 2, tile_addr, in_addr, bar);
             if (ln == 0) {
+                item_fetch(p, &pmap, &wmap0, &wmap1, &wmap2, l0, h, 2, tile_addr, in_addr, bar);
                 const uint16_t* pr0 = p.proj + (size_t)l0 * p.T * kGdnProjN;
                 nb_raw = bf2f(pr0[kOffB + h]);
                 na_raw = bf2f(pr0[kOffA + h]);
@@ -201,10 +204,10 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
         float winA[3], winB[3];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
-            winA[j] = bf2f(in_s[(3 + j * 3 + kindA) * 128 + c]);
-            winB[j] = bf2f(in_s[(3 + j * 3 + 2) * 128 + c]);
+            winA[j] = bf2f(in_s[(4 + j * 3 + kindA) * 128 + c]);
+            winB[j] = bf2f(in_s[(4 + j * 3 + 2) * 128 + c]);
         }
-        const float z_cur = bf2f(in_s[12 * 128 + c]);
+        const float z_cur = bf2f(in_s[3 * 128 + c]);
         if (tid == 128) { scal_s[0] = nb_raw; scal_s[1] = na_raw; }
         // Every thread has its copy: the buffers are free again.  Only warp 4, which issues the next
         // fetch, waits for that; the others announce it and go on.
@@ -212,8 +215,8 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
             asm volatile("bar.sync 2, 256;\n" ::: "memory");
             const int nxt = lane_id + lane_stride;
             if (nxt < p.lanes) {
-                item_fetch_part(p, nxt, h, ln, 3, tile_addr, in_addr, bar);
                 if (ln == 0) {
+                    item_fetch(p, &pmap, &wmap0, &wmap1, &wmap2, nxt, h, 3, tile_addr, in_addr, bar);
                     const uint16_t* prn = p.proj + (size_t)nxt * p.T * kGdnProjN;
                     nb_raw = bf2f(prn[kOffB + h]);
                     na_raw = bf2f(prn[kOffA + h]);
@@ -339,6 +342,71 @@ __global__ void __launch_bounds__(256, 2) gdn_step_kernel(GdnParams p) {
     if (!is_qv && pend) gated_norm(z_pend, row_pend);      // the last item's norm
 }
 
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// Tensor maps are pure functions of (base pointer, row count); a step uses the same few every time.
+struct MapKey {
+    const void* base;
+    long long rows;
+    int kind;
+    bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && kind == o.kind; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.base) ^ (std::hash<long long>()(k.rows) * 1315423911u) ^ (size_t)k.kind;
+    }
+};
+
+// kind 0: projection rows [rows][8224] bf16 seen as {2048 inner, 4 pieces 2048 apart, rows}: box = the
+//         128 values of one head in each of q, k, v, z.
+// kind 1: conv windows [lanes][3 rows][6144] bf16 seen as {2048 inner, 3 kinds, 3 rows, lanes}: box = the
+//         128 values of one head in each of the 3 x 3 (row, kind) pieces.
+bool small_input_map(CUtensorMap* out, const uint16_t* base, long long rows, int kind) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, kind};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return true; }
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr || base == nullptr || rows <= 0) return false;
+    CUresult r;
+    if (kind == 0) {
+        cuuint64_t dims[3] = {2048, 4, (cuuint64_t)rows};
+        cuuint64_t strides[2] = {2048 * 2, (cuuint64_t)kGdnProjN * 2};
+        cuuint32_t box[3] = {128, 4, 1}, elem[3] = {1, 1, 1};
+        r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<uint16_t*>(base), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        cuuint64_t dims[4] = {2048, 3, 3, (cuuint64_t)rows};
+        cuuint64_t strides[3] = {2048 * 2, (cuuint64_t)kConvCh * 2, (cuuint64_t)3 * kConvCh * 2};
+        cuuint32_t box[4] = {128, 3, 3, 1}, elem[4] = {1, 1, 1, 1};
+        r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<uint16_t*>(base), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return false;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return true;
+}
+
+}  // namespace
+
 cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
     if (p.lanes <= 0 || p.T <= 0 || p.lanes > 65535) return cudaErrorInvalidValue;
     if (p.checkpoint < 0 || p.checkpoint >= kStateBufs) return cudaErrorInvalidValue;
@@ -362,7 +430,14 @@ cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
     }
     const int items = p.lanes * kGdnHeads;
     const int grid = items < max_ctas ? items : max_ctas;
-    return launch_k(gdn_step_kernel, dim3(grid), dim3(256), kGdnSmemBytes, st, p);
+    CUtensorMap pmap, wmap[kStateBufs];
+    if (!small_input_map(&pmap, p.proj, (long long)p.lanes * p.T, 0)) return cudaErrorInvalidValue;
+    if (!small_input_map(&wmap[0], p.win[0], p.lanes, 1)) return cudaErrorInvalidValue;
+    for (int b = 1; b < kStateBufs; ++b) {
+        if (p.win[b] == nullptr) wmap[b] = wmap[0];
+        else if (!small_input_map(&wmap[b], p.win[b], p.lanes, 1)) return cudaErrorInvalidValue;
+    }
+    return launch_k(gdn_step_kernel, dim3(grid), dim3(256), kGdnSmemBytes, st, p, pmap, wmap[0], wmap[1], wmap[2]);
 }
 
 }  // namespace q35
