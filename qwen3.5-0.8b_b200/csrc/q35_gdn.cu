@@ -22,6 +22,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <unordered_map>
 
 #include "q35_common.cuh"
@@ -378,6 +379,8 @@ struct MapKeyHash {
 //         128 values of one head in each of the 3 x 3 (row, kind) pieces.
 bool small_input_map(CUtensorMap* out, const uint16_t* base, long long rows, int kind) {
     static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;                       // engines of several host threads share this cache
+    std::lock_guard<std::mutex> lock(mu);
     const MapKey key{base, rows, kind};
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return true; }
