@@ -21,6 +21,7 @@
 #include <cstdlib>
 
 #include "q35_common.cuh"
+#include "q35_async.cuh"
 
 namespace q35 {
 
@@ -216,28 +217,6 @@ constexpr int kTileBytes = kKvPage * kHeadDim * 2;        // one kv head's slice
 constexpr int kRing = 2;
 constexpr int kTmaThreads = 288;                          // 8 consumer warps + 1 producer warp
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    unsigned long long t0 = 0;
-    for (int it = 0;; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            " selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (it == 0) t0 = global_ns();
-        else if (global_ns() - t0 > 1000000000ull) return false;
-    }
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -1010,26 +989,11 @@ size_t attn_tma_smem(int ctx_pad) {
     return 1024 + (size_t)kRing * kTileBytes + 4 * kHeadDim * 4 + (size_t)8 * ctx_pad * 4 + (size_t)4 * ctx_pad * 2;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 }  // namespace
 
 // Tensor map of a K or V page pool seen as a matrix [n_pages * 128 rows][256] bf16, box 64 x 64.
 bool attn_make_pool_map(void* map_out, const uint16_t* pool, long long n_pages) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr || n_pages <= 0) return false;
     cuuint64_t dims[2] = {(cuuint64_t)kHeadDim, (cuuint64_t)n_pages * kKvHeads * kKvPage};
     cuuint64_t strides[1] = {(cuuint64_t)kHeadDim * 2};

@@ -26,40 +26,12 @@
 #include <unordered_map>
 
 #include "q35_common.cuh"
+#include "q35_async.cuh"
 
 namespace q35 {
 
 constexpr int kOffZ = 6144, kOffB = 8192, kOffA = 8208;
 constexpr uint32_t kTileBytes = kDk * kDv * sizeof(float);   // 65,536
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Poll the barrier's phase; give up after ~1 s.  Returns false on expiry.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-        uint32_t ok;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            " selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (global_ns() - t0 > 1000000000ull) return false;
-        __nanosleep(20);
-    }
-}
-
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
-        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
 
 constexpr int kInRows = 13;                                   // q, k, v raw | 3x3 window | z, 128 bf16 each
 constexpr uint32_t kInBytes = kInRows * 128 * sizeof(uint16_t);
@@ -345,21 +317,6 @@ gdn_step_kernel(GdnParams p, const __grid_constant__ CUtensorMap pmap, const __g
 
 namespace {
 
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
 // Tensor maps are pure functions of (base pointer, row count); a step uses the same few every time.
 struct MapKey {
     const void* base;
@@ -384,7 +341,7 @@ bool small_input_map(CUtensorMap* out, const uint16_t* base, long long rows, int
     const MapKey key{base, rows, kind};
     auto it = cache.find(key);
     if (it != cache.end()) { *out = it->second; return true; }
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr || base == nullptr || rows <= 0) return false;
     CUresult r;
     if (kind == 0) {

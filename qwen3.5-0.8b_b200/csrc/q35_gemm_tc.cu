@@ -20,6 +20,7 @@
 #include <cstdlib>
 
 #include "q35_common.cuh"
+#include "q35_async.cuh"
 
 namespace q35 {
 
@@ -30,39 +31,6 @@ constexpr int EPI_PARTIAL = 3;                       // f32 partial tile of one 
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KiB
 constexpr int NUM_THREADS = 192;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    unsigned long long t0 = 0;
-    for (int it = 0;; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-            " selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if (it == 0) t0 = global_ns();
-        else if (global_ns() - t0 > 1000000000ull) return false;
-    }
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
-}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
@@ -326,10 +294,6 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
         else if (global_ns() - t0 > 1000000000ull) return false;
     }
 }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-
 template <int STAGES, int EPI>
 __global__ void __launch_bounds__(P_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w,
@@ -488,25 +452,9 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_c
 }
 
 // ---- host side: tensor maps -------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
 // bf16 matrix [rows][K] row-major, box = 64 k-elements x box_rows rows, 128-byte swizzle, zero fill
 bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-    EncodeTiledFn fn = encode_fn();
+    EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)K * 2};

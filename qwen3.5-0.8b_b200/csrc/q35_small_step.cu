@@ -22,6 +22,7 @@
 // barrier atomics), which on this two-die part cost more than a kernel boundary saves.  The engine
 // therefore takes this kernel only when Q35_SMALL_STEP=1.
 #include "q35_common.cuh"
+#include "q35_async.cuh"
 
 namespace q35 {
 
@@ -33,11 +34,6 @@ constexpr int XLD2 = 2048 + 8;
 constexpr int XLD3 = kFF + 8;
 constexpr size_t kSmallSmem = (size_t)16 * XLD3 * 2;      // largest x tile: 16 rows of the SwiGLU act
 
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
     asm volatile(
