@@ -61,6 +61,14 @@ def test_bad_arguments_are_refused_without_cuda(lib):
     assert lib.q35_state_sizes_of(0, 10, null) == 1
     assert lib.q35_op_gdn_step(one, one, one, one, one, one, one, one, 70000, 1, null) == 1
     assert lib.q35_state_export_lane(null, 0, null, null, null, null, 0, null) == 1
+    # the entry points of depth-k rounds and of the bound resynchronisation
+    assert lib.q35_mtp_state_reserve_depth(null, 2) == 1
+    assert lib.q35_mtp_draft_k(null, null, null, null, null, 2, null, null) == 1
+    assert lib.q35_mtp_verify_k(null, null, null, null, null, 2, null, null, null, null) == 1
+    assert b"q35_mtp_verify_k" in lib.q35_last_error()
+    assert lib.q35_state_sync_bound(null, null) == 1
+    assert lib.q35_mtp_state_sync_bound(null, null) == 1
+    assert lib.q35_lm_head_argmax_static(null, null, 248320, 1, null, null) == 1
 
 
 def test_engine_requires_gpu(pkg):
