@@ -12,6 +12,8 @@
 //       Rows past T are padded with beta = 0, g = 0, q = k = v = 0 (they neither read nor write S).
 // The reference engine ships only the sequential span kernel (engine/gdn_rec_reg16_kernels.h); its
 // chunked prototype is disabled (engine/kernels_gdn.cpp:430-446).
+#include <cstdlib>
+
 #include "q35_common.cuh"
 
 namespace q35 {
@@ -397,6 +399,490 @@ gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__
         reinterpret_cast<float4*>(S_g)[i] = reinterpret_cast<const float4*>(S_s)[i];
 }
 
+
+// ---- (2') the chunk scan on the tensor pipe ------------------------------------------------------
+// Same algebra, but every product runs as warp-level mma: G and P from the bf16 tiles
+// (m16n8k16, exact products), the f32 products as split-TF32 (m16n8k8): an f32 operand x is fed as
+// hi = x with the low 13 mantissa bits cleared and lo = x - hi, and a.b ~ a_lo b_hi + a_hi b_lo +
+// a_hi b_hi (relative error ~2^-20 per product); q and k are bf16 values, exact as TF32, so their
+// products need two instructions.  The unit-lower-triangular solve is blocked: the four 16x16
+// diagonal blocks are inverted by forward substitution (64 threads, 16 short rows each), then each
+// warp walks the four block rows of its own 32 right-hand-side columns,
+//   X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c),
+// with both products on the tensor pipe.  Row strides are chosen so that fragment loads are
+// conflict-free (A-type rows: stride = 4 mod 32 words, B-type rows: stride = 8 mod 32 words).
+// The 64 KiB state arrives by cp.async while the chunk's scalars, G, P and the solve are computed.
+constexpr int S_LD = 136;              // f32 row stride of the state (B operand)
+constexpr int V_LD = 136;              // f32 row stride of nv / v_new (B operand)
+constexpr int KC_LD = 132;             // f32 row stride of kc (A operand)
+constexpr size_t kChunkTcSmem = (size_t)128 * S_LD * 4 + (size_t)C * V_LD * 4 + (size_t)C * KC_LD * 4 +
+                                2 * (size_t)C * KQ_LD * 2 + 3 * (size_t)C * T_LD * 4 + 8 * C * 4 + 2 * C * 4;
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// x = hi + lo exactly; hi carries the top 11 significand bits, lo the rest (the pipe reads its top 11)
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+    hi = __float_as_uint(x) & 0xffffe000u;
+    lo = __float_as_uint(__fsub_rn(x, __uint_as_float(hi)));
+}
+
+// Split-TF32 products of one A fragment against NT B tiles (b0 = B[k0 + t][n], b1 = B[k0 + t + 4][n], tiles
+// 8 columns apart, optional row scales), pass by pass so that no two consecutive instructions share an accumulator.
+template <int NT, bool A_EXACT>
+__device__ __forceinline__ void mma_row(float (&acc)[NT][4], const uint32_t (&ahi)[4], const uint32_t (&alo)[4],
+                                        const float* __restrict__ b_row0, const float* __restrict__ b_row1,
+                                        float w0, float w1) {
+    uint32_t bh[NT][2], bl[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        split_tf32(b_row0[8 * nt] * w0, bh[nt][0], bl[nt][0]);
+        split_tf32(b_row1[8 * nt] * w1, bh[nt][1], bl[nt][1]);
+    }
+    if (!A_EXACT) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma_tf32(acc[nt], alo, bh[nt][0], bh[nt][1]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mma_tf32(acc[nt], ahi, bl[nt][0], bl[nt][1]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mma_tf32(acc[nt], ahi, bh[nt][0], bh[nt][1]);
+}
+
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__ A_log,
+                    const uint16_t* __restrict__ dt_bias, const uint16_t* __restrict__ norm_w,
+                    float* __restrict__ S0, float* __restrict__ S1, float* __restrict__ S2,
+                    const int* __restrict__ sel, uint16_t* __restrict__ y, int T) {
+    extern __shared__ __align__(16) unsigned char smem_chunk[];
+    float* S_s = reinterpret_cast<float*>(smem_chunk);                 // [128][136]  S[dk][dv]
+    float* V_s = S_s + 128 * S_LD;                                     // [64][136]   nv, then v_new
+    float* KC_s = V_s + C * V_LD;                                      // [64][132]   kc
+    uint16_t* K_s = reinterpret_cast<uint16_t*>(KC_s + C * KC_LD);     // [64][136] bf16
+    uint16_t* Q_s = K_s + C * KQ_LD;                                   // [64][136] bf16
+    float* Tri_s = reinterpret_cast<float*>(Q_s + C * KQ_LD);          // [64][68]
+    float* Int_s = Tri_s + C * T_LD;                                   // [64][68]
+    float* Tinv_s = Int_s + C * T_LD;                                  // [64][68]   inverses of the diagonal blocks
+    float* sc = Tinv_s + C * T_LD;                                     // 8 x [64] row scalars
+    float* red_s = sc + 8 * C;                                         // [2][64] sum of squares per column half
+    float* cum_s = sc;
+    float* beta_s = sc + 64;
+    float* kinv_s = sc + 128;
+    float* qsc_s = sc + 192;
+    float* ecum_s = sc + 256;
+    float* kout_s = sc + 320;
+    float* g_s = sc + 384;
+    float* qn_s = sc + 448;
+
+    const int h = blockIdx.x, lane_id = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
+    const int g = ln >> 2, t = ln & 3;                 // fragment coordinates of this lane
+    const int live = sel != nullptr ? sel[lane_id] : 0;
+    float* S_g = (live == 0 ? S0 : (live == 1 ? S1 : S2)) + ((size_t)lane_id * kGdnHeads + h) * (kDk * kDv);
+    const float negA = -expf(bf2f(A_log[h]));
+    const float dtb = bf2f(dt_bias[h]);
+    const float q_scale = 0.08838834764831845f;
+
+    for (int i = tid; i < 128 * 32; i += 256)       // lands while the first chunk's scalars, G, P and solve run
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n"
+                     ::"r"(smem_addr(S_s + (i >> 5) * S_LD + (i & 31) * 4)), "l"(S_g + 4 * i) : "memory");
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+
+    const int n_chunks = (T + C - 1) / C;
+    for (int ck = 0; ck < n_chunks; ++ck) {
+        const int t0 = ck * C;
+        const int valid = (T - t0) < C ? (T - t0) : C;
+        const uint16_t* pr0 = proj + ((size_t)lane_id * T + t0) * kGdnProjN;
+
+        // ---- load q, k tiles (bf16, zero rows past T) and the gate inputs -------------------------
+        for (int i = tid; i < C * 16; i += 256) {
+            const int r = i >> 4, cc = i & 15;
+            uint4 kq = make_uint4(0, 0, 0, 0), qq = make_uint4(0, 0, 0, 0);
+            if (r < valid) {
+                const uint16_t* pr = pr0 + (size_t)r * kGdnProjN;
+                qq = *reinterpret_cast<const uint4*>(pr + h * 128 + cc * 8);
+                kq = *reinterpret_cast<const uint4*>(pr + 2048 + h * 128 + cc * 8);
+            }
+            *reinterpret_cast<uint4*>(K_s + r * KQ_LD + cc * 8) = kq;
+            *reinterpret_cast<uint4*>(Q_s + r * KQ_LD + cc * 8) = qq;
+        }
+        if (tid < C) {
+            float beta = 0.f, gg = 0.f;
+            if (tid < valid) {
+                const uint16_t* pr = pr0 + (size_t)tid * kGdnProjN;
+                beta = sigmoid_acc(bf2f(pr[kOffB + h]));
+                const float sp_in = bf2f(pr[kOffA + h]) + dtb;
+                const float sp = sp_in > 20.0f ? sp_in : log1pf(expf(sp_in));
+                gg = __fmul_rn(negA, sp);
+            }
+            beta_s[tid] = beta;
+            g_s[tid] = gg;
+        }
+        __syncthreads();
+
+        // ---- row scalars: L2 norms (warp w takes rows 8w..8w+7), prefix sum of g -----------------
+        float my_qinv[8];
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+            const int r = warp * 8 + rr;
+            const uint2 kv = *reinterpret_cast<const uint2*>(K_s + r * KQ_LD + ln * 4);
+            const uint2 qv = *reinterpret_cast<const uint2*>(Q_s + r * KQ_LD + ln * 4);
+            float ks = lo_bf(kv.x) * lo_bf(kv.x) + hi_bf(kv.x) * hi_bf(kv.x) + lo_bf(kv.y) * lo_bf(kv.y) + hi_bf(kv.y) * hi_bf(kv.y);
+            float qs = lo_bf(qv.x) * lo_bf(qv.x) + hi_bf(qv.x) * hi_bf(qv.x) + lo_bf(qv.y) * lo_bf(qv.y) + hi_bf(qv.y) * hi_bf(qv.y);
+            ks = warp_sum(ks);
+            qs = warp_sum(qs);
+            my_qinv[rr] = rsqrt_acc(qs + 1e-6f);
+            if (ln == 0) kinv_s[r] = rsqrt_acc(ks + 1e-6f);
+        }
+        if (tid == 0) {                      // sequential like the reference's cumsum, but from registers
+            float gv[C];
+#pragma unroll
+            for (int i4 = 0; i4 < C / 4; ++i4) {
+                const float4 v = reinterpret_cast<const float4*>(g_s)[i4];
+                gv[4 * i4] = v.x; gv[4 * i4 + 1] = v.y; gv[4 * i4 + 2] = v.z; gv[4 * i4 + 3] = v.w;
+            }
+            float c = 0.f;
+#pragma unroll
+            for (int i = 0; i < C; ++i) { c += gv[i]; gv[i] = c; }
+#pragma unroll
+            for (int i4 = 0; i4 < C / 4; ++i4)
+                reinterpret_cast<float4*>(cum_s)[i4] = make_float4(gv[4 * i4], gv[4 * i4 + 1], gv[4 * i4 + 2], gv[4 * i4 + 3]);
+        }
+        __syncthreads();
+        {
+            const float cumC = cum_s[C - 1];
+            if (ln < 8) {
+                const int r = warp * 8 + ln;
+                float qi = my_qinv[0];
+#pragma unroll
+                for (int rr = 1; rr < 8; ++rr) qi = ln == rr ? my_qinv[rr] : qi;     // every lane holds all 8 (warp_sum)
+                const float e = expf(cum_s[r]);
+                ecum_s[r] = e;
+                qn_s[r] = __fmul_rn(qi, q_scale);
+                qsc_s[r] = __fmul_rn(__fmul_rn(qi, q_scale), e);
+                kout_s[r] = __fmul_rn(kinv_s[r], expf(cumC - cum_s[r]));
+            }
+        }
+        __syncthreads();
+
+        // ---- right-hand sides: nv = beta v ; kc = beta e^cum k_hat ---------------------------------
+        for (int i = tid; i < C * 16; i += 256) {
+            const int r = i >> 4, cc = i & 15;
+            float vf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, kf[8];
+            if (r < valid)
+                unpack8f(*reinterpret_cast<const uint4*>(pr0 + (size_t)r * kGdnProjN + 4096 + h * 128 + cc * 8), vf);
+            unpack8f(*reinterpret_cast<const uint4*>(K_s + r * KQ_LD + cc * 8), kf);
+            const float b = beta_s[r];
+            const float kb = __fmul_rn(__fmul_rn(kinv_s[r], b), ecum_s[r]);
+            float4* xv = reinterpret_cast<float4*>(V_s + r * V_LD + cc * 8);
+            float4* xk = reinterpret_cast<float4*>(KC_s + r * KC_LD + cc * 8);
+            xv[0] = make_float4(vf[0] * b, vf[1] * b, vf[2] * b, vf[3] * b);
+            xv[1] = make_float4(vf[4] * b, vf[5] * b, vf[6] * b, vf[7] * b);
+            xk[0] = make_float4(kf[0] * kb, kf[1] * kb, kf[2] * kb, kf[3] * kb);
+            xk[1] = make_float4(kf[4] * kb, kf[5] * kb, kf[6] * kb, kf[7] * kb);
+        }
+
+        // ---- G = K K^T (warps 0-3) and P = Q K^T (warps 4-7), rows 16 (warp & 3).., columns <= row -
+        {
+            const int mt = warp & 3, m0 = 16 * mt;
+            const bool is_p = warp >= 4;
+            const uint32_t a_base = smem_addr(is_p ? Q_s : K_s) + (uint32_t)((m0 + (ln & 15)) * KQ_LD + (ln >> 4) * 8) * 2u;
+            const uint32_t b_base = smem_addr(K_s) + (uint32_t)(((ln & 7) + (ln >> 4) * 8) * KQ_LD + ((ln >> 3) & 1) * 8) * 2u;
+            float acc[4][2][4];
+#pragma unroll
+            for (int np = 0; np < 4; ++np)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc[np][0][e] = 0.f; acc[np][1][e] = 0.f; }
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                ldsm4(a, a_base + ks * 32);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    if (np <= mt) {
+                        uint32_t b[4];
+                        ldsm4(b, b_base + (uint32_t)(np * 16 * KQ_LD) * 2u + ks * 32);
+                        mma_bf16_16816(acc[np][0], a, b[0], b[1]);
+                        mma_bf16_16816(acc[np][1], a, b[2], b[3]);
+                    }
+                }
+            }
+            float* dst = is_p ? Int_s : Tri_s;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int i = m0 + g + 8 * half;
+                const float ci = cum_s[i];
+                const float gi = __fmul_rn(beta_s[i], kinv_s[i]);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    if (np <= mt) {
+#pragma unroll
+                        for (int n2 = 0; n2 < 2; ++n2) {
+                            float out2[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int j = 16 * np + 8 * n2 + 2 * t + e;
+                                const float a = acc[np][n2][2 * half + e];
+                                float v = 0.f;
+                                if (j <= i) {
+                                    const float dec = expf(ci - cum_s[j]);
+                                    const float kj = kinv_s[j];
+                                    if (is_p) v = a * kj * dec;              // times the q row scale below
+                                    else if (j < i) v = a * gi * kj * dec;
+                                }
+                                out2[e] = v;
+                            }
+                            *reinterpret_cast<float2*>(dst + i * T_LD + 16 * np + 8 * n2 + 2 * t) = make_float2(out2[0], out2[1]);
+                        }
+                    }
+                }
+            }
+        }
+        __syncthreads();
+
+        // ---- solve (I + L) X = B, X = [nv | kc]: (a) invert the four 16 x 16 diagonal blocks ------------
+        if (tid < 64) {
+            const int b16 = (tid >> 4) * 16, c = tid & 15;            // thread = column c of block b16 / 16
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = 0.f;                  // a group of four may reach past row i: times zero
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                float a0 = (i == c) ? 1.f : 0.f, a1 = 0.f;
+#pragma unroll
+                for (int j4 = 0; j4 < 4; ++j4) {                      // entries at and right of the diagonal are zero
+                    if (4 * j4 >= i) break;
+                    const float4 tr = *reinterpret_cast<const float4*>(Tri_s + (b16 + i) * T_LD + b16 + 4 * j4);
+                    a0 -= tr.x * x[4 * j4];
+                    a1 -= tr.y * x[4 * j4 + 1];
+                    a0 -= tr.z * x[4 * j4 + 2];
+                    a1 -= tr.w * x[4 * j4 + 3];
+                }
+                x[i] = a0 + a1;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) Tinv_s[(b16 + i) * T_LD + b16 + c] = x[i];
+        }
+        asm volatile("cp.async.wait_all;\n" ::: "memory");          // this thread's part of the state has landed
+        __syncthreads();
+
+        // ---- (b) block rows: X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c); a warp owns 32 columns ---------
+        {
+            float* X = warp < 4 ? (V_s + 32 * warp) : (KC_s + 32 * (warp - 4));
+            const int ld = warp < 4 ? V_LD : KC_LD;
+#pragma unroll 1
+            for (int b = 0; b < 4; ++b) {
+                float r[4][4];
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float2 v0 = *reinterpret_cast<const float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t);
+                    const float2 v1 = *reinterpret_cast<const float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t);
+                    r[nt][0] = v0.x; r[nt][1] = v0.y; r[nt][2] = v1.x; r[nt][3] = v1.y;
+                }
+                const float* Lr = Tri_s + (16 * b + g) * T_LD + t;
+#pragma unroll 1
+                for (int k0 = 0; k0 < 16 * b; k0 += 8) {              // minus L_bc X_c: the A fragment carries the sign
+                    uint32_t ahi[4], alo[4];
+                    split_tf32(-Lr[k0], ahi[0], alo[0]);
+                    split_tf32(-Lr[8 * T_LD + k0], ahi[1], alo[1]);
+                    split_tf32(-Lr[k0 + 4], ahi[2], alo[2]);
+                    split_tf32(-Lr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
+                    mma_row<4, false>(r, ahi, alo, X + (k0 + t) * ld + g, X + (k0 + t + 4) * ld + g, 1.f, 1.f);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {                      // the residual becomes a B operand: through shared memory
+                    *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
+                    *reinterpret_cast<float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t) = make_float2(r[nt][2], r[nt][3]);
+                    r[nt][0] = 0.f; r[nt][1] = 0.f; r[nt][2] = 0.f; r[nt][3] = 0.f;
+                }
+                __syncwarp();
+                const float* Dr = Tinv_s + (16 * b + g) * T_LD + 16 * b + t;
+#pragma unroll
+                for (int k0 = 0; k0 < 16; k0 += 8) {
+                    uint32_t ahi[4], alo[4];
+                    split_tf32(Dr[k0], ahi[0], alo[0]);
+                    split_tf32(Dr[8 * T_LD + k0], ahi[1], alo[1]);
+                    split_tf32(Dr[k0 + 4], ahi[2], alo[2]);
+                    split_tf32(Dr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
+                    mma_row<4, false>(r, ahi, alo, X + (16 * b + k0 + t) * ld + g, X + (16 * b + k0 + t + 4) * ld + g, 1.f, 1.f);
+                }
+                __syncwarp();
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
+                    *reinterpret_cast<float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t) = make_float2(r[nt][2], r[nt][3]);
+                }
+                __syncwarp();
+            }
+        }
+        __syncthreads();
+
+        const int mt = warp & 3, m0 = 16 * mt, nb = (warp >> 2) * 64;   // phases D, E: 16 rows x 64 columns per warp
+        // ---- v_new = nv - kc S ------------------------------------------------------------------
+        {
+            float acc[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+            const float* Ar = KC_s + (m0 + g) * KC_LD + t;
+            const float* Br = S_s + t * S_LD + nb + g;
+#pragma unroll 2
+            for (int ks = 0; ks < 16; ++ks) {
+                const int k0 = 8 * ks;
+                uint32_t ahi[4], alo[4];
+                split_tf32(Ar[k0], ahi[0], alo[0]);
+                split_tf32(Ar[8 * KC_LD + k0], ahi[1], alo[1]);
+                split_tf32(Ar[k0 + 4], ahi[2], alo[2]);
+                split_tf32(Ar[8 * KC_LD + k0 + 4], ahi[3], alo[3]);
+                mma_row<8, false>(acc, ahi, alo, Br + k0 * S_LD, Br + (k0 + 4) * S_LD, 1.f, 1.f);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float2* p0 = reinterpret_cast<float2*>(V_s + (m0 + g) * V_LD + nb + 8 * nt + 2 * t);
+                float2* p1 = reinterpret_cast<float2*>(V_s + (m0 + g + 8) * V_LD + nb + 8 * nt + 2 * t);
+                float2 v0 = *p0, v1 = *p1;
+                v0.x -= acc[nt][0]; v0.y -= acc[nt][1];
+                v1.x -= acc[nt][2]; v1.y -= acc[nt][3];
+                *p0 = v0; *p1 = v1;
+            }
+        }
+        __syncthreads();
+
+        // ---- o = (q row-scaled) S + intra v_new ; gated RMSNorm ; store y -------------------------
+        {
+            float acc[8][4], acc2[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc[nt][e] = 0.f; acc2[nt][e] = 0.f; }
+            // the epilogue's gate and weight values: asked for now, used after the products
+            uint32_t zreg[2][8], wreg[8];
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = m0 + g + 8 * half;
+                const uint16_t* zr = pr0 + (size_t)(r < valid ? r : 0) * kGdnProjN + kOffZ + h * 128 + nb + 2 * t;
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) zreg[half][nt] = *reinterpret_cast<const uint32_t*>(zr + 8 * nt);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) wreg[nt] = *reinterpret_cast<const uint32_t*>(norm_w + nb + 8 * nt + 2 * t);
+            const uint16_t* Qr = Q_s + (m0 + g) * KQ_LD + t;
+            const float* Br = S_s + t * S_LD + nb + g;
+#pragma unroll 2
+            for (int ks = 0; ks < 16; ++ks) {
+                const int k0 = 8 * ks;
+                uint32_t a[4];
+                a[0] = (uint32_t)Qr[k0] << 16;
+                a[1] = (uint32_t)Qr[8 * KQ_LD + k0] << 16;
+                a[2] = (uint32_t)Qr[k0 + 4] << 16;
+                a[3] = (uint32_t)Qr[8 * KQ_LD + k0 + 4] << 16;
+                mma_row<8, true>(acc, a, a, Br + k0 * S_LD, Br + (k0 + 4) * S_LD, 1.f, 1.f);
+            }
+            // intra rows only reach columns m <= row; rows of this warp end at m0 + 15
+            const float* Ir = Int_s + (m0 + g) * T_LD + t;
+            const float* Vr = V_s + t * V_LD + nb + g;
+#pragma unroll 1
+            for (int ks = 0; ks < 2 * mt + 2; ++ks) {
+                const int k0 = 8 * ks;
+                uint32_t ahi[4], alo[4];
+                split_tf32(Ir[k0], ahi[0], alo[0]);
+                split_tf32(Ir[8 * T_LD + k0], ahi[1], alo[1]);
+                split_tf32(Ir[k0 + 4], ahi[2], alo[2]);
+                split_tf32(Ir[8 * T_LD + k0 + 4], ahi[3], alo[3]);
+                mma_row<8, false>(acc2, ahi, alo, Vr + k0 * V_LD, Vr + (k0 + 4) * V_LD, 1.f, 1.f);
+            }
+            // o = e^cum * qinv*scale * (q~ S)  +  qinv*scale * sum_m (q~.k_m kinv_m e^(cum_r-cum_m)) v_new[m]
+            const int r0 = m0 + g, r1 = r0 + 8;
+            const float qf0 = qsc_s[r0], qn0 = qn_s[r0], qf1 = qsc_s[r1], qn1 = qn_s[r1];
+            float ss0 = 0.f, ss1 = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                acc[nt][0] = acc[nt][0] * qf0 + acc2[nt][0] * qn0;
+                acc[nt][1] = acc[nt][1] * qf0 + acc2[nt][1] * qn0;
+                acc[nt][2] = acc[nt][2] * qf1 + acc2[nt][2] * qn1;
+                acc[nt][3] = acc[nt][3] * qf1 + acc2[nt][3] * qn1;
+                ss0 += acc[nt][0] * acc[nt][0] + acc[nt][1] * acc[nt][1];
+                ss1 += acc[nt][2] * acc[nt][2] + acc[nt][3] * acc[nt][3];
+            }
+            ss0 += __shfl_xor_sync(0xffffffffu, ss0, 1); ss0 += __shfl_xor_sync(0xffffffffu, ss0, 2);
+            ss1 += __shfl_xor_sync(0xffffffffu, ss1, 1); ss1 += __shfl_xor_sync(0xffffffffu, ss1, 2);
+            if (t == 0) { red_s[(warp >> 2) * C + r0] = ss0; red_s[(warp >> 2) * C + r1] = ss1; }
+            __syncthreads();                  // also: every read of S by this phase is done
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = half == 0 ? r0 : r1;
+                if (r < valid) {
+                    const float rinv = rsqrt_acc((red_s[r] + red_s[C + r]) * (1.0f / 128.0f) + kEps);
+                    uint16_t* yr = y + ((size_t)lane_id * T + t0 + r) * kValueDim + h * 128 + nb + 2 * t;
+#pragma unroll
+                    for (int nt = 0; nt < 8; ++nt) {
+                        const uint32_t zv = zreg[half][nt], wv = wreg[nt];
+                        float n0 = __fmul_rn(acc[nt][2 * half], rinv), n1 = __fmul_rn(acc[nt][2 * half + 1], rinv);
+                        n0 = __fmul_rn(lo_bf(wv), n0);
+                        n1 = __fmul_rn(hi_bf(wv), n1);
+                        *reinterpret_cast<uint32_t*>(yr + 8 * nt) =
+                            pack_bf2(__fmul_rn(n0, silu_acc(lo_bf(zv))), __fmul_rn(n1, silu_acc(hi_bf(zv))));
+                    }
+                }
+            }
+        }
+
+        // ---- S = e^cumC S + k_hat^T (e^(cumC - cum) v_new)   (warp: 16 rows of S, all 128 columns) --
+        {
+            const int d0 = 16 * warp;
+            const float cd = expf(cum_s[C - 1]);
+            float acc[16][4];
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) {
+                const float2 s0 = *reinterpret_cast<const float2*>(S_s + (d0 + g) * S_LD + 8 * nt + 2 * t);
+                const float2 s1 = *reinterpret_cast<const float2*>(S_s + (d0 + g + 8) * S_LD + 8 * nt + 2 * t);
+                acc[nt][0] = s0.x * cd; acc[nt][1] = s0.y * cd; acc[nt][2] = s1.x * cd; acc[nt][3] = s1.y * cd;
+            }
+            const uint16_t* Kr = K_s + t * KQ_LD + d0 + g;
+            const float* Vr = V_s + t * V_LD + g;
+            float (&acc_lo)[8][4] = *reinterpret_cast<float (*)[8][4]>(&acc[0]);
+            float (&acc_hi)[8][4] = *reinterpret_cast<float (*)[8][4]>(&acc[8]);
+#pragma unroll 2
+            for (int ks = 0; ks < 8; ++ks) {
+                const int k0 = 8 * ks;
+                uint32_t a[4];
+                a[0] = (uint32_t)Kr[k0 * KQ_LD] << 16;
+                a[1] = (uint32_t)Kr[k0 * KQ_LD + 8] << 16;
+                a[2] = (uint32_t)Kr[(k0 + 4) * KQ_LD] << 16;
+                a[3] = (uint32_t)Kr[(k0 + 4) * KQ_LD + 8] << 16;
+                const float w0 = kout_s[k0 + t], w1 = kout_s[k0 + t + 4];
+                mma_row<8, true>(acc_lo, a, a, Vr + k0 * V_LD, Vr + (k0 + 4) * V_LD, w0, w1);
+                mma_row<8, true>(acc_hi, a, a, Vr + k0 * V_LD + 64, Vr + (k0 + 4) * V_LD + 64, w0, w1);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) {
+                *reinterpret_cast<float2*>(S_s + (d0 + g) * S_LD + 8 * nt + 2 * t) = make_float2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<float2*>(S_s + (d0 + g + 8) * S_LD + 8 * nt + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
+            }
+        }
+        __syncthreads();
+    }
+
+    for (int i = tid; i < 128 * 32; i += 256)
+        reinterpret_cast<float4*>(S_g)[i] = *reinterpret_cast<const float4*>(S_s + (i >> 5) * S_LD + (i & 31) * 4);
+}
+
 }  // namespace
 
 cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
@@ -405,14 +891,25 @@ cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
     if (!attr_done) {
         cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kChunkSmem);
         if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(gdn_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kChunkTcSmem);
+        if (e != cudaSuccess) return e;
         attr_done = true;
     }
     gdn_conv_prep_kernel<<<dim3(p.lanes, kConvCh / 512), 256, 0, st>>>(const_cast<uint16_t*>(p.proj), p.conv_w, p.win[0],
                                                                   p.win[1], p.win[2], p.sel, p.T);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    gdn_chunk_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w, p.S[0],
-                                                                       p.S[1], p.S[2], p.sel, p.y, p.T);
+    static int simt = -1;                           // Q35_GDN_CHUNK=simt keeps the f32 SIMT form
+    if (simt < 0) {
+        const char* env = std::getenv("Q35_GDN_CHUNK");
+        simt = (env != nullptr && env[0] == 's') ? 1 : 0;
+    }
+    if (simt)
+        gdn_chunk_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w, p.S[0],
+                                                                           p.S[1], p.S[2], p.sel, p.y, p.T);
+    else
+        gdn_chunk_tc_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkTcSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w,
+                                                                                p.S[0], p.S[1], p.S[2], p.sel, p.y, p.T);
     return cudaGetLastError();
 }
 

@@ -215,27 +215,31 @@ def test_determinism_lane_independence_and_graph(eng, pkg, golden):
 def test_small_step_kernel_matches_multi_kernel_path(pkg, weights, golden, monkeypatch, lanes):
     """At <= 16 lanes one persistent kernel runs the whole step.  Against the multi-kernel path on the
     same prompts: same positions, final-norm rows within the cascade band (the two paths sum their
-    dot products in different orders), same GDN state in layer 0 to 1e-3, and mostly equal tokens."""
+    dot products in different orders), same GDN state in layer 0 to 5e-3, and equal tokens wherever
+    the multi-kernel path's top-2 logit margin exceeds twice the largest logit difference of that row
+    (on random-init weights the margins are tiny, so a share of equal tokens means nothing at 1 lane)."""
     g = golden["config0_greedy"]
     gen = torch.Generator().manual_seed(31 + lanes)
     ids = torch.randint(0, 248320, (lanes, 70), generator=gen).int()
     ids[0, :64] = torch.from_numpy(g["prompt"]).int()
     ids = ids.cuda()
     outs = {}
+    head = weights[pkg.weights.LM + "embed_tokens.weight"].cuda().float()
     for mode in ("0", "1"):               # the multi-kernel run goes first; its tokens are fed to both
         monkeypatch.setenv("Q35_SMALL_STEP", mode)
         e = pkg.Engine(weights, max_rows=2048)
         st = e.allocate_state(lanes, 128)
         y0, _ = e.prefill(st, ids)
-        toks, rows = [y0.clone()], []
+        toks, rows, lgs = [y0.clone()], [], []
         cur = y0
         for _ in range(6):
             nrm = torch.empty((lanes, 1024), dtype=torch.bfloat16, device="cuda")
             feed = cur if mode == "0" else outs["0"]["toks"][len(toks) - 1].cuda()
-            cur = e.decode_step(st, feed, normed=nrm)
+            cur = e.decode_step(st, feed, normed=nrm)         # no logits asked: that would leave the one-kernel path
             toks.append(cur.clone())
             rows.append(nrm.float().cpu())
-        outs[mode] = dict(toks=torch.stack(toks).cpu(), rows=torch.stack(rows), pos=st.positions.tolist(),
+            lgs.append((nrm.float() @ head.T).cpu())          # the tied head applied by the checker
+        outs[mode] = dict(toks=torch.stack(toks).cpu(), rows=torch.stack(rows), lg=torch.stack(lgs), pos=st.positions.tolist(),
                           S=st.export_lane(0, 128)["gdn_state"][0].cpu(), status=e.status())
         st.close()
         e.close()
@@ -248,7 +252,11 @@ def test_small_step_kernel_matches_multi_kernel_path(pkg, weights, golden, monke
     note(f"small_step_vs_multi_kernel_lanes{lanes}", [first, rel_l2(a["rows"], b["rows"]), same, rel_l2(a["S"], b["S"])])
     assert first <= 5e-2 and rel_l2(a["rows"], b["rows"]) <= CASCADE
     assert rel_l2(a["S"], b["S"]) <= 5e-3
-    assert same >= 0.6
+    top2 = b["lg"].topk(2, dim=-1).values
+    margin = top2[..., 0] - top2[..., 1]                       # [steps, lanes], multi-kernel path
+    diff = (a["lg"] - b["lg"]).abs().amax(dim=-1)
+    flipped = a["toks"][1:] != b["toks"][1:]
+    assert bool((margin[flipped] <= 2 * diff[flipped]).all())  # every flip is explained by the logit band
 
 
 def test_host_error_paths(eng, pkg):
