@@ -463,6 +463,26 @@ __device__ __forceinline__ void mma_row(float (&acc)[NT][4], const uint32_t (&ah
     for (int nt = 0; nt < NT; ++nt) mma_tf32(acc[nt], ahi, bh[nt][0], bh[nt][1]);
 }
 
+// The same with one accumulator set per pass (summed by the caller): three times the independent
+// chains, for the short dependent products of the blocked solve.
+template <int NT>
+__device__ __forceinline__ void mma_row3(float (&acc_hh)[NT][4], float (&acc_lh)[NT][4], float (&acc_hl)[NT][4],
+                                         const uint32_t (&ahi)[4], const uint32_t (&alo)[4],
+                                         const float* __restrict__ b_row0, const float* __restrict__ b_row1) {
+    uint32_t bh[NT][2], bl[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        split_tf32(b_row0[8 * nt], bh[nt][0], bl[nt][0]);
+        split_tf32(b_row1[8 * nt], bh[nt][1], bl[nt][1]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        mma_tf32(acc_lh[nt], alo, bh[nt][0], bh[nt][1]);
+        mma_tf32(acc_hl[nt], ahi, bl[nt][0], bl[nt][1]);
+        mma_tf32(acc_hh[nt], ahi, bh[nt][0], bh[nt][1]);
+    }
+}
+
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__ A_log,
                     const uint16_t* __restrict__ dt_bias, const uint16_t* __restrict__ norm_w,
@@ -519,6 +539,13 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             }
             *reinterpret_cast<uint4*>(K_s + r * KQ_LD + cc * 8) = kq;
             *reinterpret_cast<uint4*>(Q_s + r * KQ_LD + cc * 8) = qq;
+        }
+        uint4 vraw[4];                               // this thread's v pieces: asked for now, used by the right-hand sides
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + 256 * u, r = i >> 4, cc = i & 15;
+            vraw[u] = make_uint4(0, 0, 0, 0);
+            if (r < valid) vraw[u] = *reinterpret_cast<const uint4*>(pr0 + (size_t)r * kGdnProjN + 4096 + h * 128 + cc * 8);
         }
         if (tid < C) {
             float beta = 0.f, gg = 0.f;
@@ -580,11 +607,11 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         __syncthreads();
 
         // ---- right-hand sides: nv = beta v ; kc = beta e^cum k_hat ---------------------------------
-        for (int i = tid; i < C * 16; i += 256) {
-            const int r = i >> 4, cc = i & 15;
-            float vf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, kf[8];
-            if (r < valid)
-                unpack8f(*reinterpret_cast<const uint4*>(pr0 + (size_t)r * kGdnProjN + 4096 + h * 128 + cc * 8), vf);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + 256 * u, r = i >> 4, cc = i & 15;
+            float vf[8], kf[8];
+            unpack8f(vraw[u], vf);
             unpack8f(*reinterpret_cast<const uint4*>(K_s + r * KQ_LD + cc * 8), kf);
             const float b = beta_s[r];
             const float kb = __fmul_rn(__fmul_rn(kinv_s[r], b), ecum_s[r]);
@@ -598,7 +625,7 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
 
         // ---- G = K K^T (warps 0-3) and P = Q K^T (warps 4-7), rows 16 (warp & 3).., columns <= row -
         {
-            const int mt = warp & 3, m0 = 16 * mt;
+            const int mt = warp < 4 ? warp : 7 - warp, m0 = 16 * mt;    // work grows with mt: a scheduler's two warps get mt and 3 - mt
             const bool is_p = warp >= 4;
             const uint32_t a_base = smem_addr(is_p ? Q_s : K_s) + (uint32_t)((m0 + (ln & 15)) * KQ_LD + (ln >> 4) * 8) * 2u;
             const uint32_t b_base = smem_addr(K_s) + (uint32_t)(((ln & 7) + (ln >> 4) * 8) * KQ_LD + ((ln >> 3) & 1) * 8) * 2u;
@@ -686,29 +713,34 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             const int ld = warp < 4 ? V_LD : KC_LD;
 #pragma unroll 1
             for (int b = 0; b < 4; ++b) {
-                float r[4][4];
+                float r[4][4], ra[4][4], rb[4][4];
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     const float2 v0 = *reinterpret_cast<const float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t);
                     const float2 v1 = *reinterpret_cast<const float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t);
                     r[nt][0] = v0.x; r[nt][1] = v0.y; r[nt][2] = v1.x; r[nt][3] = v1.y;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { ra[nt][e] = 0.f; rb[nt][e] = 0.f; }
                 }
                 const float* Lr = Tri_s + (16 * b + g) * T_LD + t;
-#pragma unroll 1
+#pragma unroll 2
                 for (int k0 = 0; k0 < 16 * b; k0 += 8) {              // minus L_bc X_c: the A fragment carries the sign
                     uint32_t ahi[4], alo[4];
                     split_tf32(-Lr[k0], ahi[0], alo[0]);
                     split_tf32(-Lr[8 * T_LD + k0], ahi[1], alo[1]);
                     split_tf32(-Lr[k0 + 4], ahi[2], alo[2]);
                     split_tf32(-Lr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
-                    mma_row<4, false>(r, ahi, alo, X + (k0 + t) * ld + g, X + (k0 + t + 4) * ld + g, 1.f, 1.f);
+                    mma_row3<4>(r, ra, rb, ahi, alo, X + (k0 + t) * ld + g, X + (k0 + t + 4) * ld + g);
                 }
                 __syncwarp();
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {                      // the residual becomes a B operand: through shared memory
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) r[nt][e] += ra[nt][e] + rb[nt][e];
                     *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
                     *reinterpret_cast<float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t) = make_float2(r[nt][2], r[nt][3]);
-                    r[nt][0] = 0.f; r[nt][1] = 0.f; r[nt][2] = 0.f; r[nt][3] = 0.f;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { r[nt][e] = 0.f; ra[nt][e] = 0.f; rb[nt][e] = 0.f; }
                 }
                 __syncwarp();
                 const float* Dr = Tinv_s + (16 * b + g) * T_LD + 16 * b + t;
@@ -719,11 +751,13 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                     split_tf32(Dr[8 * T_LD + k0], ahi[1], alo[1]);
                     split_tf32(Dr[k0 + 4], ahi[2], alo[2]);
                     split_tf32(Dr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
-                    mma_row<4, false>(r, ahi, alo, X + (16 * b + k0 + t) * ld + g, X + (16 * b + k0 + t + 4) * ld + g, 1.f, 1.f);
+                    mma_row3<4>(r, ra, rb, ahi, alo, X + (16 * b + k0 + t) * ld + g, X + (16 * b + k0 + t + 4) * ld + g);
                 }
                 __syncwarp();
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) r[nt][e] += ra[nt][e] + rb[nt][e];
                     *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
                     *reinterpret_cast<float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t) = make_float2(r[nt][2], r[nt][3]);
                 }
@@ -732,7 +766,7 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         }
         __syncthreads();
 
-        const int mt = warp & 3, m0 = 16 * mt, nb = (warp >> 2) * 64;   // phases D, E: 16 rows x 64 columns per warp
+        const int mt = warp < 4 ? warp : 7 - warp, m0 = 16 * mt, nb = (warp >> 2) * 64;   // 16 rows x 64 columns per warp
         // ---- v_new = nv - kc S ------------------------------------------------------------------
         {
             float acc[8][4];
@@ -836,8 +870,9 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                         float n0 = __fmul_rn(acc[nt][2 * half], rinv), n1 = __fmul_rn(acc[nt][2 * half + 1], rinv);
                         n0 = __fmul_rn(lo_bf(wv), n0);
                         n1 = __fmul_rn(hi_bf(wv), n1);
+                        const float z0 = lo_bf(zv), z1 = hi_bf(zv);      // SiLU with the fast exp / divide: the bf16 cast hides their 2 ulp
                         *reinterpret_cast<uint32_t*>(yr + 8 * nt) =
-                            pack_bf2(__fmul_rn(n0, silu_acc(lo_bf(zv))), __fmul_rn(n1, silu_acc(hi_bf(zv))));
+                            pack_bf2(__fmul_rn(n0, __fdividef(z0, 1.0f + __expf(-z0))), __fmul_rn(n1, __fdividef(z1, 1.0f + __expf(-z1))));
                     }
                 }
             }
