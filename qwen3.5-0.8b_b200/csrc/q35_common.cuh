@@ -221,6 +221,7 @@ cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st);
 // columns of p.proj with the conv outputs
 constexpr int kGdnChunkMinT = 32;
 cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st);
+cudaError_t gdn_chunk_init(cudaStream_t st);    // per-device lookup table of the chunked prefill; idempotent
 
 struct AttnParams {
     const uint16_t* proj;      // [lanes*T][5120]

@@ -339,6 +339,7 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     e->max_rows = cfg->max_rows;
     e->embed = w->embed;
     CK(attn_init());
+    CK(gdn_chunk_init(st));
     CK(dev_alloc(e->allocs, &e->final_norm, (size_t)kHidden));
     CK(copy_rows(e->final_norm, w->final_norm, kHidden, st));
     e->weight_bytes = 2LL * e->vocab * kHidden + 2LL * kHidden;

@@ -29,46 +29,78 @@ constexpr int kOffZ = 6144, kOffB = 8192, kOffA = 8208;
 constexpr size_t kChunkSmem = (size_t)128 * 128 * 4 + (size_t)C * X_LD * 4 + 2 * (size_t)C * KQ_LD * 2 +
                               2 * (size_t)C * T_LD * 4 + 8 * C * 4;
 
+// SiLU of a bf16 value rounded to bf16 is a function of 16 bits: the conv pass, which is bound by
+// instruction issue (an accurate exp and an IEEE divide per element), looks it up instead.  The
+// table is filled on the device by the same expression the step kernel evaluates, so both agree bit
+// for bit; 128 KiB, hot lines stay in L1.
+__device__ uint16_t g_silu_bf16[65536];
+__global__ void silu_table_kernel() {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    g_silu_bf16[b] = f2bf(silu_acc(bf2f((uint16_t)b)));
+}
+
 // ---- (1) conv + SiLU over a lane's T rows, in place; window roll -------------------------------
-// grid (lanes, 12), 256 threads, 2 adjacent channels per thread.
-__global__ void __launch_bounds__(256)
+// grid (lanes, 6), 128 threads, 8 adjacent channels per thread (16-byte loads, eight rows in flight).
+__global__ void __launch_bounds__(128)
 gdn_conv_prep_kernel(uint16_t* __restrict__ proj, const uint16_t* __restrict__ conv_w,
                      uint16_t* __restrict__ win0, uint16_t* __restrict__ win1, uint16_t* __restrict__ win2,
                      const int* __restrict__ sel, int T) {
     const int lane_id = blockIdx.x;
-    const int c = (blockIdx.y * 256 + threadIdx.x) * 2;
+    const int c = (blockIdx.y * 128 + threadIdx.x) * 8;
     const int live = sel != nullptr ? sel[lane_id] : 0;
     uint16_t* win = (live == 0 ? win0 : (live == 1 ? win1 : win2)) + (size_t)lane_id * 3 * kConvCh;
-    float tap[2][4], w[2][3];
-    {
-        const uint4 tw = *reinterpret_cast<const uint4*>(conv_w + (size_t)c * 4);
-        tap[0][0] = lo_bf(tw.x); tap[0][1] = hi_bf(tw.x); tap[0][2] = lo_bf(tw.y); tap[0][3] = hi_bf(tw.y);
-        tap[1][0] = lo_bf(tw.z); tap[1][1] = hi_bf(tw.z); tap[1][2] = lo_bf(tw.w); tap[1][3] = hi_bf(tw.w);
+    float tap[8][4], w[8][3];
 #pragma unroll
-        for (int j = 0; j < 3; ++j) {
-            const uint32_t v = *reinterpret_cast<const uint32_t*>(win + j * kConvCh + c);
-            w[0][j] = lo_bf(v); w[1][j] = hi_bf(v);
-        }
+    for (int q = 0; q < 4; ++q) {            // taps of channels 2q, 2q + 1
+        const uint4 tw = *reinterpret_cast<const uint4*>(conv_w + (size_t)(c + 2 * q) * 4);
+        tap[2 * q][0] = lo_bf(tw.x); tap[2 * q][1] = hi_bf(tw.x); tap[2 * q][2] = lo_bf(tw.y); tap[2 * q][3] = hi_bf(tw.y);
+        tap[2 * q + 1][0] = lo_bf(tw.z); tap[2 * q + 1][1] = hi_bf(tw.z); tap[2 * q + 1][2] = lo_bf(tw.w); tap[2 * q + 1][3] = hi_bf(tw.w);
+    }
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(win + j * kConvCh + c);
+        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { w[2 * q][j] = lo_bf(vw[q]); w[2 * q + 1][j] = hi_bf(vw[q]); }
     }
     uint16_t* p = proj + (size_t)lane_id * T * kGdnProjN + c;
-#pragma unroll 4
-    for (int t = 0; t < T; ++t, p += kGdnProjN) {
-        const uint32_t rv = *reinterpret_cast<const uint32_t*>(p);
-        const float raw[2] = {lo_bf(rv), hi_bf(rv)};
-        float u[2];
+    for (int t0 = 0; t0 < T; t0 += 8) {
+        uint4 rv[8];
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            float acc = __fmul_rn(w[e][0], tap[e][0]);
-            acc = __fadd_rn(acc, __fmul_rn(w[e][1], tap[e][1]));
-            acc = __fadd_rn(acc, __fmul_rn(w[e][2], tap[e][2]));
-            acc = __fadd_rn(acc, __fmul_rn(raw[e], tap[e][3]));
-            u[e] = bfround(silu_acc(bfround(acc)));
-            w[e][0] = w[e][1]; w[e][1] = w[e][2]; w[e][2] = raw[e];
+        for (int u = 0; u < 8; ++u)
+            if (t0 + u < T) rv[u] = *reinterpret_cast<const uint4*>(p + (size_t)(t0 + u) * kGdnProjN);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (t0 + u < T) {
+                const uint32_t rw[4] = {rv[u].x, rv[u].y, rv[u].z, rv[u].w};
+                uint32_t ow[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float o2[2];
+#pragma unroll
+                    for (int e2 = 0; e2 < 2; ++e2) {
+                        const int e = 2 * q + e2;
+                        const float raw = e2 == 0 ? lo_bf(rw[q]) : hi_bf(rw[q]);
+                        float acc = __fmul_rn(w[e][0], tap[e][0]);
+                        acc = __fadd_rn(acc, __fmul_rn(w[e][1], tap[e][1]));
+                        acc = __fadd_rn(acc, __fmul_rn(w[e][2], tap[e][2]));
+                        acc = __fadd_rn(acc, __fmul_rn(raw, tap[e][3]));
+                        o2[e2] = bf2f(g_silu_bf16[f2bf(acc)]);             // = bfround(silu(bfround(acc)))
+                        w[e][0] = w[e][1]; w[e][1] = w[e][2]; w[e][2] = raw;
+                    }
+                    ow[q] = pack_bf2(o2[0], o2[1]);
+                }
+                *reinterpret_cast<uint4*>(p + (size_t)(t0 + u) * kGdnProjN) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
         }
-        *reinterpret_cast<uint32_t*>(p) = pack_bf2(u[0], u[1]);
     }
 #pragma unroll
-    for (int j = 0; j < 3; ++j) *reinterpret_cast<uint32_t*>(win + j * kConvCh + c) = pack_bf2(w[0][j], w[1][j]);
+    for (int j = 0; j < 3; ++j) {
+        uint32_t ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) ow[q] = pack_bf2(w[2 * q][j], w[2 * q + 1][j]);
+        *reinterpret_cast<uint4*>(win + j * kConvCh + c) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
 }
 
 __device__ __forceinline__ void unpack8f(const uint4& v, float (&f)[8]) {
@@ -517,52 +549,60 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
     const float dtb = bf2f(dt_bias[h]);
     const float q_scale = 0.08838834764831845f;
 
-    for (int i = tid; i < 128 * 32; i += 256)       // lands while the first chunk's scalars, G, P and solve run
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n"
-                     ::"r"(smem_addr(S_s + (i >> 5) * S_LD + (i & 31) * 4)), "l"(S_g + 4 * i) : "memory");
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-
     const int n_chunks = (T + C - 1) / C;
     for (int ck = 0; ck < n_chunks; ++ck) {
         const int t0 = ck * C;
         const int valid = (T - t0) < C ? (T - t0) : C;
         const uint16_t* pr0 = proj + ((size_t)lane_id * T + t0) * kGdnProjN;
 
-        // ---- load q, k tiles (bf16, zero rows past T) and the gate inputs -------------------------
+        // ---- q, k tiles (bf16, zero rows past T), v pieces and gate inputs: the small requests go out first,
+        // the 64 KiB state behind them; it lands while the scalars, G, P and the solve are computed ---------
         for (int i = tid; i < C * 16; i += 256) {
             const int r = i >> 4, cc = i & 15;
-            uint4 kq = make_uint4(0, 0, 0, 0), qq = make_uint4(0, 0, 0, 0);
-            if (r < valid) {
-                const uint16_t* pr = pr0 + (size_t)r * kGdnProjN;
-                qq = *reinterpret_cast<const uint4*>(pr + h * 128 + cc * 8);
-                kq = *reinterpret_cast<const uint4*>(pr + 2048 + h * 128 + cc * 8);
-            }
-            *reinterpret_cast<uint4*>(K_s + r * KQ_LD + cc * 8) = kq;
-            *reinterpret_cast<uint4*>(Q_s + r * KQ_LD + cc * 8) = qq;
+            const uint16_t* pr = pr0 + (size_t)(r < valid ? r : 0) * kGdnProjN + h * 128 + cc * 8;
+            const uint32_t n = r < valid ? 16u : 0u;                // 0 bytes read = 16 bytes of zeros written
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+                         ::"r"(smem_addr(Q_s + r * KQ_LD + cc * 8)), "l"(pr), "r"(n) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
+                         ::"r"(smem_addr(K_s + r * KQ_LD + cc * 8)), "l"(pr + 2048), "r"(n) : "memory");
         }
-        uint4 vraw[4];                               // this thread's v pieces: asked for now, used by the right-hand sides
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        uint4 vraw[4];                               // this thread's v pieces, used by the right-hand sides
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int i = tid + 256 * u, r = i >> 4, cc = i & 15;
             vraw[u] = make_uint4(0, 0, 0, 0);
             if (r < valid) vraw[u] = *reinterpret_cast<const uint4*>(pr0 + (size_t)r * kGdnProjN + 4096 + h * 128 + cc * 8);
         }
+        float b_in = 0.f, a_in = 0.f;
+        if (tid < valid) {
+            const uint16_t* pr = pr0 + (size_t)tid * kGdnProjN;
+            b_in = bf2f(pr[kOffB + h]);
+            a_in = bf2f(pr[kOffA + h]);
+        }
+        if (ck == 0) {
+            for (int i = tid; i < 128 * 32; i += 256)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n"
+                             ::"r"(smem_addr(S_s + (i >> 5) * S_LD + (i & 31) * 4)), "l"(S_g + 4 * i) : "memory");
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        }
         if (tid < C) {
             float beta = 0.f, gg = 0.f;
             if (tid < valid) {
-                const uint16_t* pr = pr0 + (size_t)tid * kGdnProjN;
-                beta = sigmoid_acc(bf2f(pr[kOffB + h]));
-                const float sp_in = bf2f(pr[kOffA + h]) + dtb;
+                beta = sigmoid_acc(b_in);
+                const float sp_in = a_in + dtb;
                 const float sp = sp_in > 20.0f ? sp_in : log1pf(expf(sp_in));
                 gg = __fmul_rn(negA, sp);
             }
             beta_s[tid] = beta;
             g_s[tid] = gg;
         }
+        if (ck == 0) asm volatile("cp.async.wait_group 1;\n" ::: "memory");     // the q, k tiles; the state may still fly
+        else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         __syncthreads();
 
         // ---- row scalars: L2 norms (warp w takes rows 8w..8w+7), prefix sum of g -----------------
-        float my_qinv[8];
+        float my_qs = 0.f, my_ks = 0.f;              // lane rr keeps the sums of row 8 warp + rr
 #pragma unroll
         for (int rr = 0; rr < 8; ++rr) {
             const int r = warp * 8 + rr;
@@ -572,8 +612,12 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             float qs = lo_bf(qv.x) * lo_bf(qv.x) + hi_bf(qv.x) * hi_bf(qv.x) + lo_bf(qv.y) * lo_bf(qv.y) + hi_bf(qv.y) * hi_bf(qv.y);
             ks = warp_sum(ks);
             qs = warp_sum(qs);
-            my_qinv[rr] = rsqrt_acc(qs + 1e-6f);
-            if (ln == 0) kinv_s[r] = rsqrt_acc(ks + 1e-6f);
+            if (ln == rr) { my_ks = ks; my_qs = qs; }
+        }
+        float my_qinv = 0.f;
+        if (ln < 8) {
+            my_qinv = rsqrt_acc(my_qs + 1e-6f);
+            kinv_s[warp * 8 + ln] = rsqrt_acc(my_ks + 1e-6f);
         }
         if (tid == 0) {                      // sequential like the reference's cumsum, but from registers
             float gv[C];
@@ -594,9 +638,7 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             const float cumC = cum_s[C - 1];
             if (ln < 8) {
                 const int r = warp * 8 + ln;
-                float qi = my_qinv[0];
-#pragma unroll
-                for (int rr = 1; rr < 8; ++rr) qi = ln == rr ? my_qinv[rr] : qi;     // every lane holds all 8 (warp_sum)
+                const float qi = my_qinv;
                 const float e = expf(cum_s[r]);
                 ecum_s[r] = e;
                 qn_s[r] = __fmul_rn(qi, q_scale);
@@ -920,6 +962,21 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
 
 }  // namespace
 
+// Fills the SiLU table of the current device on `st` (once per device; an engine does it at creation,
+// a bare operator call at its first use, ordered ahead of the conv pass on the same stream).
+cudaError_t gdn_chunk_init(cudaStream_t st) {
+    static bool table_done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (table_done[dev]) return cudaSuccess;
+    silu_table_kernel<<<256, 256, 0, st>>>();
+    e = cudaGetLastError();
+    if (e == cudaSuccess) table_done[dev] = true;
+    return e;
+}
+
 cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
     if (p.lanes <= 0 || p.T <= 0 || p.lanes > 65535 || p.checkpoint) return cudaErrorInvalidValue;
     static bool attr_done = false;
@@ -930,7 +987,11 @@ cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
         if (e != cudaSuccess) return e;
         attr_done = true;
     }
-    gdn_conv_prep_kernel<<<dim3(p.lanes, kConvCh / 512), 256, 0, st>>>(const_cast<uint16_t*>(p.proj), p.conv_w, p.win[0],
+    {
+        cudaError_t e = gdn_chunk_init(st);         // no-op once this device's table is filled
+        if (e != cudaSuccess) return e;
+    }
+    gdn_conv_prep_kernel<<<dim3(p.lanes, kConvCh / 1024), 128, 0, st>>>(const_cast<uint16_t*>(p.proj), p.conv_w, p.win[0],
                                                                   p.win[1], p.win[2], p.sel, p.T);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
