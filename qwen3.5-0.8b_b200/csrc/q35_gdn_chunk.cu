@@ -445,9 +445,8 @@ gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__
 // conflict-free (A-type rows: stride = 4 mod 32 words, B-type rows: stride = 8 mod 32 words).
 // The 64 KiB state arrives by cp.async while the chunk's scalars, G, P and the solve are computed.
 constexpr int S_LD = 136;              // f32 row stride of the state (B operand)
-constexpr int V_LD = 136;              // f32 row stride of nv / v_new (B operand)
-constexpr int KC_LD = 132;             // f32 row stride of kc (A operand)
-constexpr size_t kChunkTcSmem = (size_t)128 * S_LD * 4 + (size_t)C * V_LD * 4 + (size_t)C * KC_LD * 4 +
+constexpr int V_LD = 136;              // f32 row stride of the right-hand side / v_new (B operand)
+constexpr size_t kChunkTcSmem = (size_t)128 * S_LD * 4 + (size_t)C * V_LD * 4 +
                                 2 * (size_t)C * KQ_LD * 2 + 3 * (size_t)C * T_LD * 4 + 8 * C * 4 + 2 * C * 4;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -495,6 +494,23 @@ __device__ __forceinline__ void mma_row(float (&acc)[NT][4], const uint32_t (&ah
     for (int nt = 0; nt < NT; ++nt) mma_tf32(acc[nt], ahi, bh[nt][0], bh[nt][1]);
 }
 
+// Two exact (bf16-valued) A fragments against the same NT B tiles: the split of B is shared.
+template <int NT>
+__device__ __forceinline__ void mma_row_pair(float (&acc0)[NT][4], float (&acc1)[NT][4], const uint32_t (&a0)[4],
+                                             const uint32_t (&a1)[4], const float* __restrict__ b_row0,
+                                             const float* __restrict__ b_row1) {
+    uint32_t bh[NT][2], bl[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        split_tf32(b_row0[8 * nt], bh[nt][0], bl[nt][0]);
+        split_tf32(b_row1[8 * nt], bh[nt][1], bl[nt][1]);
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { mma_tf32(acc0[nt], a0, bl[nt][0], bl[nt][1]); mma_tf32(acc1[nt], a1, bl[nt][0], bl[nt][1]); }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) { mma_tf32(acc0[nt], a0, bh[nt][0], bh[nt][1]); mma_tf32(acc1[nt], a1, bh[nt][0], bh[nt][1]); }
+}
+
 // The same with one accumulator set per pass (summed by the caller): three times the independent
 // chains, for the short dependent products of the blocked solve.
 template <int NT>
@@ -522,9 +538,8 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                     const int* __restrict__ sel, uint16_t* __restrict__ y, int T) {
     extern __shared__ __align__(16) unsigned char smem_chunk[];
     float* S_s = reinterpret_cast<float*>(smem_chunk);                 // [128][136]  S[dk][dv]
-    float* V_s = S_s + 128 * S_LD;                                     // [64][136]   nv, then v_new
-    float* KC_s = V_s + C * V_LD;                                      // [64][132]   kc
-    uint16_t* K_s = reinterpret_cast<uint16_t*>(KC_s + C * KC_LD);     // [64][136] bf16
+    float* V_s = S_s + 128 * S_LD;                                     // [64][136]   beta v, right-hand side, v_new
+    uint16_t* K_s = reinterpret_cast<uint16_t*>(V_s + C * V_LD);       // [64][136] bf16
     uint16_t* Q_s = K_s + C * KQ_LD;                                   // [64][136] bf16
     float* Tri_s = reinterpret_cast<float*>(Q_s + C * KQ_LD);          // [64][68]
     float* Int_s = Tri_s + C * T_LD;                                   // [64][68]
@@ -648,21 +663,16 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         }
         __syncthreads();
 
-        // ---- right-hand sides: nv = beta v ; kc = beta e^cum k_hat ---------------------------------
+        // ---- beta v into the right-hand-side tile ------------------------------------------------------
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int i = tid + 256 * u, r = i >> 4, cc = i & 15;
-            float vf[8], kf[8];
+            float vf[8];
             unpack8f(vraw[u], vf);
-            unpack8f(*reinterpret_cast<const uint4*>(K_s + r * KQ_LD + cc * 8), kf);
             const float b = beta_s[r];
-            const float kb = __fmul_rn(__fmul_rn(kinv_s[r], b), ecum_s[r]);
             float4* xv = reinterpret_cast<float4*>(V_s + r * V_LD + cc * 8);
-            float4* xk = reinterpret_cast<float4*>(KC_s + r * KC_LD + cc * 8);
             xv[0] = make_float4(vf[0] * b, vf[1] * b, vf[2] * b, vf[3] * b);
             xv[1] = make_float4(vf[4] * b, vf[5] * b, vf[6] * b, vf[7] * b);
-            xk[0] = make_float4(kf[0] * kb, kf[1] * kb, kf[2] * kb, kf[3] * kb);
-            xk[1] = make_float4(kf[4] * kb, kf[5] * kb, kf[6] * kb, kf[7] * kb);
         }
 
         // ---- G = K K^T (warps 0-3) and P = Q K^T (warps 4-7), rows 16 (warp & 3).., columns <= row -
@@ -721,9 +731,10 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                 }
             }
         }
+        asm volatile("cp.async.wait_all;\n" ::: "memory");          // this thread's part of the state has landed
         __syncthreads();
 
-        // ---- solve (I + L) X = B, X = [nv | kc]: (a) invert the four 16 x 16 diagonal blocks ------------
+        // ---- the four 16 x 16 diagonal blocks of I + L, inverted by forward substitution ----------------
         if (tid < 64) {
             const int b16 = (tid >> 4) * 16, c = tid & 15;            // thread = column c of block b16 / 16
             float x[16];
@@ -746,18 +757,59 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
 #pragma unroll
             for (int i = 0; i < 16; ++i) Tinv_s[(b16 + i) * T_LD + b16 + c] = x[i];
         }
-        asm volatile("cp.async.wait_all;\n" ::: "memory");          // this thread's part of the state has landed
+
+        // ---- q~ S and k~ S in one pass over the state (q~, k~: the raw bf16 rows; warp = 16 rows x 64 columns);
+        // then the right-hand side  beta v - (beta e^cum / |k|) (k~ S).  With T = inv(I + L) this gives
+        // v_new = T (beta v) - T (beta e^cum k_hat) S  without ever forming  T (beta e^cum k_hat) ------------
+        const int mt = warp < 4 ? warp : 7 - warp, m0 = 16 * mt, nb = (warp >> 2) * 64;
+        float acc[8][4];                                              // q~ S: kept until the output stage
+        {
+            float acck[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { acc[nt][e] = 0.f; acck[nt][e] = 0.f; }
+            const uint16_t* Qr = Q_s + (m0 + g) * KQ_LD + t;
+            const uint16_t* Kr = K_s + (m0 + g) * KQ_LD + t;
+            const float* Br = S_s + t * S_LD + nb + g;
+#pragma unroll 2
+            for (int ks = 0; ks < 16; ++ks) {
+                const int k0 = 8 * ks;
+                uint32_t aq[4], ak[4];
+                aq[0] = (uint32_t)Qr[k0] << 16;
+                aq[1] = (uint32_t)Qr[8 * KQ_LD + k0] << 16;
+                aq[2] = (uint32_t)Qr[k0 + 4] << 16;
+                aq[3] = (uint32_t)Qr[8 * KQ_LD + k0 + 4] << 16;
+                ak[0] = (uint32_t)Kr[k0] << 16;
+                ak[1] = (uint32_t)Kr[8 * KQ_LD + k0] << 16;
+                ak[2] = (uint32_t)Kr[k0 + 4] << 16;
+                ak[3] = (uint32_t)Kr[8 * KQ_LD + k0 + 4] << 16;
+                mma_row_pair<8>(acc, acck, aq, ak, Br + k0 * S_LD, Br + (k0 + 4) * S_LD);
+            }
+            const int r0 = m0 + g, r1 = r0 + 8;
+            const float kb0 = __fmul_rn(__fmul_rn(kinv_s[r0], beta_s[r0]), ecum_s[r0]);
+            const float kb1 = __fmul_rn(__fmul_rn(kinv_s[r1], beta_s[r1]), ecum_s[r1]);
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float2* p0 = reinterpret_cast<float2*>(V_s + r0 * V_LD + nb + 8 * nt + 2 * t);
+                float2* p1 = reinterpret_cast<float2*>(V_s + r1 * V_LD + nb + 8 * nt + 2 * t);
+                float2 v0 = *p0, v1 = *p1;
+                v0.x -= kb0 * acck[nt][0]; v0.y -= kb0 * acck[nt][1];
+                v1.x -= kb1 * acck[nt][2]; v1.y -= kb1 * acck[nt][3];
+                *p0 = v0; *p1 = v1;
+            }
+        }
         __syncthreads();
 
-        // ---- (b) block rows: X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c); a warp owns 32 columns ---------
+        // ---- v_new = T rhs by block rows: X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c); a warp owns 16 columns ----
         {
-            float* X = warp < 4 ? (V_s + 32 * warp) : (KC_s + 32 * (warp - 4));
-            const int ld = warp < 4 ? V_LD : KC_LD;
+            float* X = V_s + 16 * warp;
+            constexpr int ld = V_LD;
 #pragma unroll 1
             for (int b = 0; b < 4; ++b) {
-                float r[4][4], ra[4][4], rb[4][4];
+                float r[2][4], ra[2][4], rb[2][4];
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
+                for (int nt = 0; nt < 2; ++nt) {
                     const float2 v0 = *reinterpret_cast<const float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t);
                     const float2 v1 = *reinterpret_cast<const float2*>(X + (16 * b + g + 8) * ld + 8 * nt + 2 * t);
                     r[nt][0] = v0.x; r[nt][1] = v0.y; r[nt][2] = v1.x; r[nt][3] = v1.y;
@@ -772,11 +824,11 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                     split_tf32(-Lr[8 * T_LD + k0], ahi[1], alo[1]);
                     split_tf32(-Lr[k0 + 4], ahi[2], alo[2]);
                     split_tf32(-Lr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
-                    mma_row3<4>(r, ra, rb, ahi, alo, X + (k0 + t) * ld + g, X + (k0 + t + 4) * ld + g);
+                    mma_row3<2>(r, ra, rb, ahi, alo, X + (k0 + t) * ld + g, X + (k0 + t + 4) * ld + g);
                 }
                 __syncwarp();
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {                      // the residual becomes a B operand: through shared memory
+                for (int nt = 0; nt < 2; ++nt) {                      // the residual becomes a B operand: through shared memory
 #pragma unroll
                     for (int e = 0; e < 4; ++e) r[nt][e] += ra[nt][e] + rb[nt][e];
                     *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
@@ -793,11 +845,11 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
                     split_tf32(Dr[8 * T_LD + k0], ahi[1], alo[1]);
                     split_tf32(Dr[k0 + 4], ahi[2], alo[2]);
                     split_tf32(Dr[8 * T_LD + k0 + 4], ahi[3], alo[3]);
-                    mma_row3<4>(r, ra, rb, ahi, alo, X + (16 * b + k0 + t) * ld + g, X + (16 * b + k0 + t + 4) * ld + g);
+                    mma_row3<2>(r, ra, rb, ahi, alo, X + (16 * b + k0 + t) * ld + g, X + (16 * b + k0 + t + 4) * ld + g);
                 }
                 __syncwarp();
 #pragma unroll
-                for (int nt = 0; nt < 4; ++nt) {
+                for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
                     for (int e = 0; e < 4; ++e) r[nt][e] += ra[nt][e] + rb[nt][e];
                     *reinterpret_cast<float2*>(X + (16 * b + g) * ld + 8 * nt + 2 * t) = make_float2(r[nt][0], r[nt][1]);
@@ -808,45 +860,13 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         }
         __syncthreads();
 
-        const int mt = warp < 4 ? warp : 7 - warp, m0 = 16 * mt, nb = (warp >> 2) * 64;   // 16 rows x 64 columns per warp
-        // ---- v_new = nv - kc S ------------------------------------------------------------------
-        {
-            float acc[8][4];
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-            const float* Ar = KC_s + (m0 + g) * KC_LD + t;
-            const float* Br = S_s + t * S_LD + nb + g;
-#pragma unroll 2
-            for (int ks = 0; ks < 16; ++ks) {
-                const int k0 = 8 * ks;
-                uint32_t ahi[4], alo[4];
-                split_tf32(Ar[k0], ahi[0], alo[0]);
-                split_tf32(Ar[8 * KC_LD + k0], ahi[1], alo[1]);
-                split_tf32(Ar[k0 + 4], ahi[2], alo[2]);
-                split_tf32(Ar[8 * KC_LD + k0 + 4], ahi[3], alo[3]);
-                mma_row<8, false>(acc, ahi, alo, Br + k0 * S_LD, Br + (k0 + 4) * S_LD, 1.f, 1.f);
-            }
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                float2* p0 = reinterpret_cast<float2*>(V_s + (m0 + g) * V_LD + nb + 8 * nt + 2 * t);
-                float2* p1 = reinterpret_cast<float2*>(V_s + (m0 + g + 8) * V_LD + nb + 8 * nt + 2 * t);
-                float2 v0 = *p0, v1 = *p1;
-                v0.x -= acc[nt][0]; v0.y -= acc[nt][1];
-                v1.x -= acc[nt][2]; v1.y -= acc[nt][3];
-                *p0 = v0; *p1 = v1;
-            }
-        }
-        __syncthreads();
-
         // ---- o = (q row-scaled) S + intra v_new ; gated RMSNorm ; store y -------------------------
         {
-            float acc[8][4], acc2[8][4];
+            float acc2[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { acc[nt][e] = 0.f; acc2[nt][e] = 0.f; }
+                for (int e = 0; e < 4; ++e) acc2[nt][e] = 0.f;
             // the epilogue's gate and weight values: asked for now, used after the products
             uint32_t zreg[2][8], wreg[8];
 #pragma unroll
@@ -858,18 +878,6 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             }
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) wreg[nt] = *reinterpret_cast<const uint32_t*>(norm_w + nb + 8 * nt + 2 * t);
-            const uint16_t* Qr = Q_s + (m0 + g) * KQ_LD + t;
-            const float* Br = S_s + t * S_LD + nb + g;
-#pragma unroll 2
-            for (int ks = 0; ks < 16; ++ks) {
-                const int k0 = 8 * ks;
-                uint32_t a[4];
-                a[0] = (uint32_t)Qr[k0] << 16;
-                a[1] = (uint32_t)Qr[8 * KQ_LD + k0] << 16;
-                a[2] = (uint32_t)Qr[k0 + 4] << 16;
-                a[3] = (uint32_t)Qr[8 * KQ_LD + k0 + 4] << 16;
-                mma_row<8, true>(acc, a, a, Br + k0 * S_LD, Br + (k0 + 4) * S_LD, 1.f, 1.f);
-            }
             // intra rows only reach columns m <= row; rows of this warp end at m0 + 15
             const float* Ir = Int_s + (m0 + g) * T_LD + t;
             const float* Vr = V_s + t * V_LD + nb + g;
