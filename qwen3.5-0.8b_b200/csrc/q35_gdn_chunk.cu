@@ -2,14 +2,20 @@
 //
 // For a body that carries T >= 32 tokens per lane the token-by-token recurrence is replaced by
 //   (1) gdn_conv_prep_kernel : causal conv1d + SiLU over all T rows of a lane, in place over the
-//       raw q|k|v columns of the projection buffer, and the conv-window roll;
-//   (2) gdn_chunk_kernel     : one CTA per (head, lane) walks the chunks with the 128x128 f32 state
+//       raw q|k|v columns of the projection buffer, and the conv-window roll (SiLU of a bf16 value
+//       by table: the pass is otherwise bound by instruction issue, not by memory);
+//   (2) gdn_chunk_tc_kernel  : one CTA per (head, lane) walks the chunks with the 128x128 f32 state
 //       resident in shared memory.  Per chunk: row scalars (L2 norms, beta, log-decay prefix sum),
-//       G = K K^T and P = Q K^T masked by the pairwise decay, ONE unit-lower-triangular solve for
-//       both right-hand sides [beta v | beta e^cum k], then
-//           v_new = nv - kc S ;  o = (e^cum q) S + intra v_new ;  S = e^cumC S + (e^(cumC-cum) k)^T v_new
-//       and the gated RMSNorm of o, all in f32 like the reference (speccheck/specimpl.py:187-235).
-//       Rows past T are padded with beta = 0, g = 0, q = k = v = 0 (they neither read nor write S).
+//       G = K K^T and P = Q K^T masked by the pairwise decay, q S and k S in one pass over the state,
+//       ONE unit-lower-triangular solve
+//           v_new = inv(I + L) (beta v - beta e^cum k_hat S),
+//           o = (e^cum q) S + intra v_new ;  S = e^cumC S + (e^(cumC-cum) k)^T v_new
+//       and the gated RMSNorm of o: the algebra of the reference's chunked form
+//       (speccheck/specimpl.py:187-235), every product on the tensor pipe with f32-grade operands
+//       (see the kernel's comment).  Rows past T are padded with beta = 0, g = 0, q = k = v = 0
+//       (they neither read nor write S).
+//       gdn_chunk_kernel is the earlier f32 SIMT form of the same scan, kept as a cross-check
+//       (Q35_GDN_CHUNK=simt): it solves for [beta v | beta e^cum k] and applies S afterwards.
 // The reference engine ships only the sequential span kernel (engine/gdn_rec_reg16_kernels.h); its
 // chunked prototype is disabled (engine/kernels_gdn.cpp:430-446).
 #include <cstdlib>
@@ -433,17 +439,22 @@ gdn_chunk_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restrict__
 
 
 // ---- (2') the chunk scan on the tensor pipe ------------------------------------------------------
-// Same algebra, but every product runs as warp-level mma: G and P from the bf16 tiles
-// (m16n8k16, exact products), the f32 products as split-TF32 (m16n8k8): an f32 operand x is fed as
-// hi = x with the low 13 mantissa bits cleared and lo = x - hi, and a.b ~ a_lo b_hi + a_hi b_lo +
-// a_hi b_hi (relative error ~2^-20 per product); q and k are bf16 values, exact as TF32, so their
-// products need two instructions.  The unit-lower-triangular solve is blocked: the four 16x16
-// diagonal blocks are inverted by forward substitution (64 threads, 16 short rows each), then each
-// warp walks the four block rows of its own 32 right-hand-side columns,
-//   X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c),
-// with both products on the tensor pipe.  Row strides are chosen so that fragment loads are
-// conflict-free (A-type rows: stride = 4 mod 32 words, B-type rows: stride = 8 mod 32 words).
-// The 64 KiB state arrives by cp.async while the chunk's scalars, G, P and the solve are computed.
+// Every product runs as warp-level mma: G and P from the bf16 tiles (m16n8k16, exact products), the
+// f32 products as split-TF32 (m16n8k8): an f32 operand x is fed as hi = x with the low 13 mantissa
+// bits cleared and lo = x - hi, and a.b ~ a_lo b_hi + a_hi b_lo + a_hi b_hi (relative error ~2^-20
+// per product); q and k are bf16 values, exact as TF32, so their products need two instructions.
+// Order of a chunk (warp = 16 rows x 64 columns of a 64 x 128 result unless said otherwise):
+//   loads (q, k by cp.async, v and gate inputs to registers; on the first chunk the 64 KiB state by
+//   cp.async behind them) -> row scalars -> beta v -> G, P -> [state landed] inverses of the four
+//   16 x 16 diagonal blocks of I + L (64 threads, forward substitution) -> q S and k S in one pass
+//   over the state -> right-hand side beta v - (beta e^cum / |k|) (k S) -> blocked solve, a warp
+//   walking the four block rows of its own 16 columns, X_b = inv(D_b) (B_b - sum_{c<b} L_bc X_c) ->
+//   intra v_new, output scaling, gated RMSNorm, y -> state update (warp = 16 rows of S).
+// Forming the right-hand side before the solve halves the solve and drops one 64 x 128 x 128
+// product against  inv(I + L) (beta e^cum k_hat).  Row strides make fragment loads conflict-free
+// (A-type rows: stride = 4 mod 32 words, B-type rows: stride = 8 mod 32 words).  Work that grows
+// with the row tile (G / P blocks, intra columns) is dealt so that the two warps of a scheduler
+// get tiles mt and 3 - mt.
 constexpr int S_LD = 136;              // f32 row stride of the state (B operand)
 constexpr int V_LD = 136;              // f32 row stride of the right-hand side / v_new (B operand)
 constexpr size_t kChunkTcSmem = (size_t)128 * S_LD * 4 + (size_t)C * V_LD * 4 +
