@@ -1014,11 +1014,8 @@ cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
                                                                   p.win[1], p.win[2], p.sel, p.T);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    static int simt = -1;                           // Q35_GDN_CHUNK=simt keeps the f32 SIMT form
-    if (simt < 0) {
-        const char* env = std::getenv("Q35_GDN_CHUNK");
-        simt = (env != nullptr && env[0] == 's') ? 1 : 0;
-    }
+    const char* env = std::getenv("Q35_GDN_CHUNK");     // "simt": the f32 SIMT form (read per call: a prefill body, not a hot loop)
+    const bool simt = env != nullptr && env[0] == 's';
     if (simt)
         gdn_chunk_kernel<<<dim3(kGdnHeads, p.lanes), 256, kChunkSmem, st>>>(p.proj, p.A_log, p.dt_bias, p.norm_w, p.S[0],
                                                                            p.S[1], p.S[2], p.sel, p.y, p.T);

@@ -282,6 +282,30 @@ def test_gdn_chunked_vs_oracle(eng, weights, lanes, T):
         assert rel_l2(y[i * T:(i + 1) * T].float(), d["y"].float()) <= 1e-2
 
 
+def test_gdn_chunked_tensor_pipe_matches_simt_form(eng, weights, monkeypatch):
+    """The scan on the tensor pipe (split-TF32 products, blocked solve) against the f32 SIMT form of
+    the same chunk algebra on the same inputs, 3 lanes x 130 rows (two full chunks + a ragged one):
+    states within 2e-5 relative, identical conv windows, gated rows within the bf16 band."""
+    l, lanes, T = 1, 3, 130
+    gen = torch.Generator().manual_seed(77)
+    h = torch.randn((lanes, T, 1024), generator=gen).to(torch.bfloat16)
+    win = torch.randn((lanes, 3, 6144), generator=gen).to(torch.bfloat16)
+    S0 = torch.randn((lanes, 16, 128, 128), generator=gen) * 0.1
+    proj = torch.stack([gdn_proj_rows(weights, l, h[i]) for i in range(lanes)]).reshape(lanes * T, -1)
+    out = {}
+    for form in ("simt", "tc"):
+        monkeypatch.setenv("Q35_GDN_CHUNK", form)
+        out[form] = gdn_device_step(eng, weights, l, proj.clone(), S0, win, lanes, T)
+    (y_a, S_a, w_a), (y_b, S_b, w_b) = out["simt"], out["tc"]
+    e_s = rel_l2(S_b, S_a)
+    e_y = rel_l2(y_b.float(), y_a.float())
+    note("gdn_chunk_tensor_pipe_vs_simt", [e_s, e_y])
+    assert e_s <= 2e-5, e_s
+    assert torch.equal(w_a, w_b)
+    assert e_y <= 4e-3, e_y
+    assert not torch.equal(S_a, S0)                     # the scan did move the state
+
+
 # ------------------------------------------------------------------------------------- attention
 def paged(K, V, pages_per_lane, lanes):
     """Scatter contiguous caches [lanes][ctx][2][256] into page pools + an (arbitrary) page table."""
