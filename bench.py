@@ -356,6 +356,8 @@ def main():
     dist = world > 1
     if dist:
         import torch.distributed as td
+        # stdout carries exactly one JSON line: NCCL's own banner ("NCCL version ...") goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         td.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_package()
     pkg.build_lib.build()
