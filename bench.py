@@ -198,7 +198,7 @@ def measure(pkg, eng, lanes: int, prompt: int, steps: int, warmup: int, dist, sa
                 ctx_mid=ctx_mid, prefill_s=prefill_s, clocks=clocks, last_tokens=cur.clone())
 
 
-def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warmup: int = 3, depth: int = 1) -> dict:
+def measure_mtp(pkg, eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warmup: int = 3, depth: int = 1) -> dict:
     """Chunk-64 prefill of `lanes` x `prompt` ids, then `rounds` speculative rounds (`depth` chained MTP
     drafts, verify of depth + 1 tokens), tokens chained on the device.  On random-init weights the
     draft almost never matches the target, so accepted tok/s is about one token per lane per round."""
@@ -211,29 +211,21 @@ def measure_mtp(eng, lanes: int = 16, prompt: int = 1024, rounds: int = 64, warm
     t, h = eng.prefill(st, ids, want_normed=True)
     torch.cuda.synchronize()
     prefill_s = time.time() - t0
-    emitted = torch.zeros((), dtype=torch.int64, device="cuda")
-
-    def one_round():
-        nonlocal t, h
-        pos = (st.positions + 1).int()
-        if depth == 1:
-            d = eng.mtp_draft(m, h, t, pos)
-            emit, n_emit, h = eng.mtp_verify(st, m, t, d)
-        else:
-            d = eng.mtp_draft_k(m, h, t, pos, depth)
-            emit, n_emit, h = eng.mtp_verify_k(st, m, t, d)
-        t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
-        return n_emit
-
+    # one captured round (drafts + verify + verdict + hand-over), replayed: nothing crosses the host between rounds
+    g = pkg.MtpRoundGraph(eng, st, m, depth=depth)
+    g.tok.copy_(t)
+    g.h.copy_(h)
     for _ in range(warmup):
-        one_round()
+        g.replay()
+    g.emitted_total.zero_()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(rounds):
-        emitted += one_round().sum()
+        g.replay()                      # the graph tallies its emitted tokens on the device
     b.record()
     torch.cuda.synchronize()
+    emitted = g.emitted_total
     ms = a.elapsed_time(b)
     n = int(emitted.item())
     if eng.status() != 0:
@@ -400,8 +392,8 @@ def main():
                           "family_ms_per_step": rf["family_ms_per_step"]})
     mtp = None
     if rank == 0 and not args.no_mtp and eng.has_mtp:
-        mtp = measure_mtp(eng)
-        mtp["depth2"] = measure_mtp(eng, depth=2)      # the reference's default round width
+        mtp = measure_mtp(pkg, eng)
+        mtp["depth2"] = measure_mtp(pkg, eng, depth=2)      # the reference's default round width
     if dist:
         import torch.distributed as td
         td.barrier()

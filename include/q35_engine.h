@@ -194,6 +194,11 @@ int q35_mtp_state_reset(q35_mtp_state* m, void* stream);
 /* The draft cache's host bound only grows (one row per draft), while a round that does not accept
  * everything drops its rows on the device: read the true lengths back and tighten the bound. */
 int q35_mtp_state_sync_bound(q35_mtp_state* m, void* stream);
+/* Host bound of the draft cache for a caller that replays a captured CUDA graph of a round: n rows
+ * per replay (the capture itself counted once); Q35_ERR_CAPACITY when the cache would overflow.  The
+ * reference reads its verdict words back every round (engine/mtp_verify.h:117-125) and needs no
+ * such bound; rounds chained on the device do. */
+int q35_mtp_state_note_advance(q35_mtp_state* m, int n);
 /* Replaces mtpdraft::draft_round (engine/mtp_draft.h:233): from the target's post-final-norm rows
  * h_norm [lanes][1024], the just-emitted tokens y_next [lanes] and the drafted positions
  * pos [lanes], propose proposal [lanes] and append one row to each lane's draft cache. */

@@ -7,4 +7,4 @@ from . import parallel  # noqa: F401
 from . import checkpoint  # noqa: F401
 from . import session  # noqa: F401
 from . import mtp_adaptive  # noqa: F401
-from .engine import Engine, LaneState, MtpState, Q35Error, StepGraph, load_library  # noqa: F401
+from .engine import Engine, LaneState, MtpRoundGraph, MtpState, Q35Error, StepGraph, load_library  # noqa: F401

@@ -7,11 +7,11 @@
 // row with 16-byte loads; the cache is addressed through a per-lane page table
 // (page = 64 positions x 2 kv heads x 256 dims).
 //
-// Two forms.  Contexts up to 1024 positions: attn_tma_kernel streams whole K and V pages (32 KiB per
+// Two forms.  Context capacities up to 3072 positions: attn_tma_kernel streams whole K and V pages (32 KiB per
 // kv head) through a two-deep shared-memory ring with TMA (128-byte swizzle), takes the scores and
 // P.V on the tensor cores (m16n8k16; q is split into bf16 hi + lo parts so the f32 rotated query
-// loses nothing, the softmax weights are bf16 by contract), and keeps two CTAs per SM so four pages
-// are in flight per SM.  Longer contexts: attn_decode_kernel (plain loads, CUDA-core dots).
+// loses nothing, the softmax weights are bf16 by contract), and keeps two CTAs per SM (up to 1024
+// positions) so four pages are in flight per SM.  Longer contexts: attn_decode_kernel (plain loads, CUDA-core dots).
 //
 // Replaces attn_decode_layer / mtp_attn_row (engine/kernels.h:730-906,
 // engine/kernels_attn.cpp:995-1068); arithmetic follows speccheck/specimpl.py:320-397 as executed,
@@ -26,7 +26,10 @@
 namespace q35 {
 
 constexpr int kAttnMaxCtx = 8192;
-constexpr int kAttnTmaMaxCtx = 1024;      // contexts up to here take the TMA + tensor-core form
+// Context capacities up to here take the TMA + tensor-core forms: their scores and weights of the whole
+// row live in shared memory (40 bytes per position beside the 64 KiB page ring), so up to 1,024
+// positions two CTAs share an SM and beyond that one CTA has it alone.
+constexpr int kAttnTmaMaxCtx = 3072;
 constexpr int kOffK = 4096, kOffV = 4608;
 
 __device__ __forceinline__ size_t kv_offset(const int* __restrict__ table, int pos, int kvh) {
@@ -209,7 +212,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(AttnParams p, int c
 
 
 // ------------------------------------------------------------------------------------------------
-// TMA + tensor-core form (contexts <= 1024)
+// TMA + tensor-core form (context capacities <= kAttnTmaMaxCtx)
 // ------------------------------------------------------------------------------------------------
 namespace {
 

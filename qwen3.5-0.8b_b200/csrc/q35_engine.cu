@@ -813,6 +813,16 @@ extern "C" int q35_mtp_state_sync_bound(q35_mtp_state* m, void* stream) {
     return Q35_OK;
 }
 
+// A caller that replays a captured CUDA graph of a speculative round reports the rows its drafts
+// append (the captured call counted once), like q35_state_note_advance for the positions.
+extern "C" int q35_mtp_state_note_advance(q35_mtp_state* m, int n) {
+    REQUIRE(m, Q35_ERR_ARG, "q35_mtp_state_note_advance: null state");
+    REQUIRE(m->host_n_hi + n <= m->max_ctx && m->host_n_hi + n >= 0, Q35_ERR_CAPACITY,
+            "draft cache rows %d + %d beyond %d", m->host_n_hi, n, m->max_ctx);
+    m->host_n_hi += n;
+    return Q35_OK;
+}
+
 extern "C" int q35_mtp_state_create(q35_engine* e, q35_state* s, int max_ctx, q35_mtp_state** out) {
     REQUIRE(e && s && out, Q35_ERR_ARG, "q35_mtp_state_create: null argument");
     REQUIRE(e->has_mtp, Q35_ERR_STATE, "engine was created without MTP weights");

@@ -277,3 +277,68 @@ def test_depth_must_be_reserved(eng, pkg, golden):
     with pytest.raises(pkg.Q35Error):
         eng.mtp_allocate(st, 32, depth=3)
     m.close(); st.close()
+
+
+@pytest.mark.parametrize("depth", [1, 2])
+def test_round_graph_equals_eager_rounds(eng, pkg, golden, depth):
+    """A replayed CUDA graph of one round against the same rounds launched one call at a time:
+    identical emitted tokens and counts every round, identical positions and layer-0 state after,
+    and the host bounds refuse a replay that could overrun the draft cache."""
+    lanes, rounds = 3, 6
+    ids = prompts(golden, lanes)
+
+    def start(cache_rows):
+        st = eng.allocate_state(lanes, 96)
+        m = eng.mtp_allocate(st, cache_rows, depth=depth)
+        t, h = eng.prefill(st, ids, want_normed=True)
+        return st, m, t, h
+
+    # eager
+    st, m, t, h = start(64)
+    eager = []
+    for _ in range(rounds):
+        pos = (st.positions + 1).int()
+        if depth == 1:
+            d = eng.mtp_draft(m, h, t, pos)
+            emit, n_emit, h = eng.mtp_verify(st, m, t, d)
+        else:
+            d = eng.mtp_draft_k(m, h, t, pos, depth)
+            emit, n_emit, h = eng.mtp_verify_k(st, m, t, d)
+        t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
+        eager.append((emit.cpu(), n_emit.cpu()))
+    pos_e = st.positions.cpu()
+    S_e = st.export_lane(0, 96)["gdn_state"][0].cpu()
+    m.close()
+    st.close()
+
+    # graph
+    st, m, t, h = start(64)
+    g = pkg.MtpRoundGraph(eng, st, m, depth=depth)
+    g.tok.copy_(t)
+    g.h.copy_(h)
+    for r in range(rounds):
+        g.replay()
+        emit, n_emit = g.emit.cpu(), g.n_emit.cpu()
+        assert torch.equal(n_emit, eager[r][1]), r
+        for i in range(lanes):
+            n = int(n_emit[i])
+            assert torch.equal(emit[i, :n], eager[r][0][i, :n]), (r, i)
+    assert torch.equal(st.positions.cpu(), pos_e)
+    assert torch.equal(st.export_lane(0, 96)["gdn_state"][0].cpu(), S_e)
+    assert int(g.emitted_total) == sum(int(n.sum()) for _, n in eager)
+    assert eng.status() == 0
+    m.close()
+    st.close()
+
+    # a cache of 2 * depth rows holds two rounds by the host's worst-case bound: the third replay is refused
+    st, m, t, h = start(2 * depth)
+    g = pkg.MtpRoundGraph(eng, st, m, depth=depth)
+    g.tok.copy_(t)
+    g.h.copy_(h)
+    g.replay()
+    g.replay()
+    with pytest.raises(pkg.Q35Error):
+        g.replay()
+    torch.cuda.synchronize()
+    m.close()
+    st.close()

@@ -410,12 +410,18 @@ def test_attn_prompt_body_vs_oracle(eng, weights, ctxs, T):
     note(f"attn_prompt_body_T{T}_lanes{lanes}_worst_rel_l2", worst)
 
 
-def test_attn_long_context_form(eng, weights):
-    """Contexts beyond 1,024 positions (the plain-load kernel; up to the 8,192-position cap) on
-    synthetic caches (keys N(0, 0.25), values N(0, 1): thousands of positions carry weight)."""
+@pytest.mark.parametrize("ctxs", [
+    [1024, 1500, 4031, 8191],                                   # capacity 8,192: the plain-load kernel
+    [1100, 2047, 2990, 1024],                                   # capacity 3,008, 4 lanes: clusters of 8 CTAs
+    [1024 + (37 * i) % 1900 for i in range(20)],                # 20 lanes: clusters of 4 CTAs
+    [1030 + (53 * i) % 1500 for i in range(34)],                # 34 lanes: one CTA per (lane, kv head), alone on its SM
+])
+def test_attn_long_context_form(eng, weights, ctxs):
+    """Contexts beyond 1,024 positions: the TMA forms up to a capacity of 3,072 positions, the
+    plain-load kernel beyond (up to the 8,192-position cap), on synthetic caches (keys N(0, 0.25),
+    values N(0, 1): thousands of positions carry weight)."""
     l = 3
     pre = f"{O.LM}layers.{l}.self_attn."
-    ctxs = [1024, 1500, 4031, 8191]
     lanes = len(ctxs)
     gen = torch.Generator().manual_seed(99)
     Ks, Vs, projs, refs = [], [], [], []
@@ -443,8 +449,9 @@ def test_attn_long_context_form(eng, weights):
         pg = int(table[i, c // 64])
         assert rel_l2(kd[pg, :, c % 64].float(), refs[i][1]) < 2e-3
         assert torch.equal(vd[pg, :, c % 64], refs[i][2])
-        note(f"attn_long_ctx{c}_rel_l2", e)
-        note(f"attn_long_ctx{c}_out_norm", float(out[i].float().norm()))
+        if lanes == 4:
+            note(f"attn_long_ctx{c}_rel_l2", e)
+            note(f"attn_long_ctx{c}_out_norm", float(out[i].float().norm()))
 
 
 def test_attn_golden(eng, weights, golden):
