@@ -10,6 +10,8 @@
 //     ldmatrix + m16n8k16, tile BM x BN chosen so that the grid covers the 148 SMs.
 // Replaces the reference's proj_group_rows / mlp_gateup / mlp_down / lm_head_gemv_* launchers
 // (engine/kernels.h:183-297,363-374,939-945) and its library GEMM route.
+#include <cstdlib>
+
 #include "q35_common.cuh"
 
 namespace q35 {
@@ -417,8 +419,22 @@ static TileChoice choose_tile(int M, int N) {
     return {32, 32};
 }
 
+// The head of <= 16 rows runs on the tcgen05 kernel too (rows past the body are zero-filled by TMA):
+// it streams the 508 MB table faster than the GEMV form (115 vs 138 us at 16 rows), and a decode
+// step and a verify body of any width then take their logits from the same instruction sequence.
+// Q35_HEAD_TC=0 keeps the GEMV form.
+static bool head_tc_few_rows() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* env = std::getenv("Q35_HEAD_TC");
+        mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    return mode == 1;
+}
+
 int linear_argmax_parts(int rows, int N) {
-    if (rows <= 16) return (N + 31) / 32;          // K = 1024 -> NB = 4 -> 32 weight rows per CTA
+    if (rows <= 16 && !(head_tc_few_rows() && N >= 128))
+        return (N + 31) / 32;                      // K = 1024 -> NB = 4 -> 32 weight rows per CTA
     return (N + 127) / 128;                        // argmax always runs BN = 128 tiles
 }
 
@@ -457,7 +473,7 @@ cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int r
         n_parts = linear_argmax_parts(rows, N);
         if (n_parts_out) *n_parts_out = n_parts;
     }
-    if (linear_tc_eligible(rows, N, K))
+    if (linear_tc_eligible(rows, N, K) || (epi == EPI_ARGMAX && head_tc_few_rows() && N >= 128 && K % 64 == 0))
         return launch_linear_tc(x, W, out, rows, N, K, epi, partials, logits, n_parts, status, st);
     switch (epi) {
         case EPI_PLAIN: return dispatch<EPI_PLAIN>(x, W, out, rows, N, K, partials, logits, n_parts, st);
