@@ -348,7 +348,10 @@ def main():
     dist = world > 1
     if dist:
         import torch.distributed as td
-        # stdout carries exactly one JSON line: NCCL's own banner ("NCCL version ...") goes to stderr
+        # stdout carries exactly one JSON line: NCCL's own banner ("NCCL version ...") goes to stderr.  NCCL
+        # honours NCCL_DEBUG_FILE only above the VERSION level, so that level is raised to WARN.
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         td.init_process_group("nccl", device_id=torch.device("cuda", local))
     pkg = load_package()
