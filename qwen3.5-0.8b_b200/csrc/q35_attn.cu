@@ -473,13 +473,12 @@ __device__ __forceinline__ float2 peer_ld_f32x2(uint32_t addr) {
 
 template <bool FUSED_APPEND>
 __global__ void __launch_bounds__(kTmaThreads, 2)
-attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ CUtensorMap kmap,
+attn_cluster_kernel(AttnParams p, int ctx_pad, int lpad, int cs, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
     if (threadIdx.x == 0) { prefetch_tensormap(&kmap); prefetch_tensormap(&vmap); }
     __shared__ float ml_s[8];                              // local max [4 heads] | local sum of exp [4]
-    __shared__ float ML_s[8];                              // the row's max | 1 / sum
     __shared__ __align__(16) float o_part[4 * kHeadDim];   // this CTA's f32 partial of P.V
     pdl_wait();
     const bool dead = p.status != nullptr && *p.status != 0;
@@ -487,8 +486,10 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (ring - smem_u32(smem_raw));
     float* q_s = reinterpret_cast<float*>(base_ptr + kRing * kTileBytes);      // [4][256]
-    float* sc2 = q_s + 4 * kHeadDim;                                           // [2][4][ctx_pad]
-    uint16_t* w_s = reinterpret_cast<uint16_t*>(sc2 + 8 * ctx_pad);            // [4][ctx_pad] bf16
+    // scores and weights of THIS CTA's pages only, page j of the CTA at [j * 64, j * 64 + 64): lpad = 64 x the
+    // most pages a CTA of the cluster can own, so the footprint falls with the cluster size
+    float* sc2 = q_s + 4 * kHeadDim;                                           // [2][4][lpad]
+    uint16_t* w_s = reinterpret_cast<uint16_t*>(sc2 + 8 * lpad);               // [4][lpad] bf16
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kRing]);
 
     const int row = blockIdx.x, kvh = blockIdx.y, rank = blockIdx.z;
@@ -602,10 +603,10 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
                 mma_bf16(sacc, a[0], a[1], a[2], a[3], blo[ks][0], blo[ks][1]);
             }
             if (t < 2) {
-                const int pos = (rank + j * cs) * kKvPage + mt * 16 + g;
-                float* s0 = sc2 + (kh * 4 + 2 * t) * ctx_pad;
-                if (pos < ctx_pad) { s0[pos] = sacc[0] * 0.0625f; s0[ctx_pad + pos] = sacc[1] * 0.0625f; }
-                if (pos + 8 < ctx_pad) { s0[pos + 8] = sacc[2] * 0.0625f; s0[ctx_pad + pos + 8] = sacc[3] * 0.0625f; }
+                const int pos = j * kKvPage + mt * 16 + g;               // local: j < myP <= lpad / 64
+                float* s0 = sc2 + (kh * 4 + 2 * t) * lpad;
+                s0[pos] = sacc[0] * 0.0625f; s0[lpad + pos] = sacc[1] * 0.0625f;
+                s0[pos + 8] = sacc[2] * 0.0625f; s0[lpad + pos + 8] = sacc[3] * 0.0625f;
             }
             __syncwarp();
             if (ln == 0) mbar_arrive(empty0 + 8 * b);
@@ -613,18 +614,18 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
         asm volatile("bar.sync 1, 256;\n" ::: "memory");
         // ---- local max and sum of exp per head over this CTA's positions ----------------------------
         if (warp < 4) {
-            const float* sa = sc2 + warp * ctx_pad;
-            const float* sb = sc2 + (4 + warp) * ctx_pad;
+            const float* sa = sc2 + warp * lpad;
+            const float* sb = sc2 + (4 + warp) * lpad;
             float m = -INFINITY;
             for (int j = 0; j < myP; ++j) {
-                const int base = (rank + j * cs) * kKvPage;
-                for (int i = base + ln; i < base + kKvPage && i < n_ctx; i += 32) m = fmaxf(m, sa[i] + sb[i]);
+                const int left = n_ctx - (rank + j * cs) * kKvPage;     // positions of this page inside the context
+                for (int o = ln; o < kKvPage && o < left; o += 32) m = fmaxf(m, sa[j * kKvPage + o] + sb[j * kKvPage + o]);
             }
             m = warp_max(m);
             float l = 0.f;
             for (int j = 0; j < myP; ++j) {
-                const int base = (rank + j * cs) * kKvPage;
-                for (int i = base + ln; i < base + kKvPage && i < n_ctx; i += 32) l += expf(sa[i] + sb[i] - m);
+                const int left = n_ctx - (rank + j * cs) * kKvPage;
+                for (int o = ln; o < kKvPage && o < left; o += 32) l += expf(sa[j * kKvPage + o] + sb[j * kKvPage + o] - m);
             }
             l = warp_sum(l);
             if (ln == 0) { ml_s[warp] = m; ml_s[4 + warp] = l; }
@@ -645,13 +646,15 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
             const float mr = peer_ld_f32(peer_addr(&ml_s[warp], r)), lr = peer_ld_f32(peer_addr(&ml_s[4 + warp], r));
             if (lr > 0.f) L += lr * expf(mr - M);
         }
-        const float* sa = sc2 + warp * ctx_pad;
-        const float* sb = sc2 + (4 + warp) * ctx_pad;
-        uint16_t* w = w_s + warp * ctx_pad;
+        const float* sa = sc2 + warp * lpad;
+        const float* sb = sc2 + (4 + warp) * lpad;
+        uint16_t* w = w_s + warp * lpad;
         for (int j = 0; j < myP; ++j) {
-            const int base = (rank + j * cs) * kKvPage;
-            for (int i = base + ln; i < base + kKvPage && i < ctx_pad; i += 32)
-                w[i] = i < n_ctx ? f2bf(__fdiv_rn(expf(sa[i] + sb[i] - M), L)) : (uint16_t)0;
+            const int left = n_ctx - (rank + j * cs) * kKvPage;
+            for (int o = ln; o < kKvPage; o += 32) {
+                const int i = j * kKvPage + o;
+                w[i] = o < left ? f2bf(__fdiv_rn(expf(sa[i] + sb[i] - M), L)) : (uint16_t)0;
+            }
         }
     }
     if (warp < 8) {
@@ -663,11 +666,11 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int cs, const __grid_constant__ C
             const uint32_t tile = ring + b * kTileBytes;
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks) {
-                const int p0 = (rank + j * cs) * kKvPage + ks * 16;
+                const int p0 = j * kKvPage + ks * 16;
                 uint32_t a0 = 0, a2 = 0;
-                if (g < 4 && p0 + 16 <= ctx_pad) {
-                    a0 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 2 * t);
-                    a2 = *reinterpret_cast<const uint32_t*>(w_s + g * ctx_pad + p0 + 8 + 2 * t);
+                if (g < 4) {
+                    a0 = *reinterpret_cast<const uint32_t*>(w_s + g * lpad + p0 + 2 * t);
+                    a2 = *reinterpret_cast<const uint32_t*>(w_s + g * lpad + p0 + 8 + 2 * t);
                 }
 #pragma unroll
                 for (int np = 0; np < 2; ++np) {
@@ -1091,7 +1094,8 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
             cudaLaunchConfig_t cfg{};
             cfg.gridDim = dim3(rows, kKvHeads, cs);
             cfg.blockDim = dim3(kTmaThreads);
-            cfg.dynamicSmemBytes = smem;
+            const int lpad = ((pad64 / kKvPage + cs - 1) / cs) * kKvPage;      // positions a CTA of the cluster can own
+            cfg.dynamicSmemBytes = attn_tma_smem(lpad);
             cfg.stream = st;
             cudaLaunchAttribute at[2];
             at[0].id = cudaLaunchAttributeClusterDimension;
@@ -1102,8 +1106,8 @@ cudaError_t launch_attn(const AttnParams& p, cudaStream_t st) {
             at[1].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = at;
             cfg.numAttrs = pdl_enabled() ? 2 : 1;
-            if (p.T == 1) return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true>, p, pad64, cs, kmap, vmap);
-            return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false>, p, pad64, cs, kmap, vmap);
+            if (p.T == 1) return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<true>, p, pad64, lpad, cs, kmap, vmap);
+            return cudaLaunchKernelEx(&cfg, attn_cluster_kernel<false>, p, pad64, lpad, cs, kmap, vmap);
         }
         if (p.T == 1) return launch_k(attn_tma_kernel<true>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
         return launch_k(attn_tma_kernel<false>, grid, dim3(kTmaThreads), smem, st, p, pad64, kmap, vmap);
