@@ -16,7 +16,9 @@ constants, `Tracker::note` for the state machine):
 The reference bills a round 1.58 (depth 1) / 1.90 (depth 2) plain steps, midpoints of bands it
 measured on its own hardware (engine/mtp_adaptive.h:58-76).  Measured here on B200 at 16 lanes
 (bench.py, configs[4]): 2.06 ms and 2.22 ms per round against a 1.14 ms plain step = 1.81 and 1.95,
-which are this module's defaults; billing a round dearer than it is only demotes a little early.
+which are this module's defaults; billing a round dearer than it is only demotes a little early
+(later kernel work brought the rounds to 1.57 / 1.93 ms as replayed graphs, `engine.MtpRoundGraph`,
+and the plain step to 1.11 ms; the call-by-call rounds this loop issues sit in between).
 
 The reference feeds its tracker from the verdict words it reads back every round.  Rounds here are
 chained on the device with no host round trip, so `speculate()` reads the emitted counts back once
