@@ -515,9 +515,15 @@ class MtpRoundGraph:
     worst case per replay (depth + 1 positions, depth draft rows); `state.sync_bound()` /
     `mtp.sync_bound()` tighten them when the caller synchronises anyway."""
 
-    def __init__(self, engine: Engine, state: LaneState, mtp: MtpState, depth: int = 1):
+    def __init__(self, engine: Engine, state: LaneState, mtp: MtpState, depth: int = 1, history: int = 0):
         L = state.lanes
         self.engine, self.state, self.mtp, self.depth = engine, state, mtp, depth
+        # optional ring of the last `history` rounds' verdicts, written by the graph itself (slot = rounds % history),
+        # for a caller that reads verdicts back every few rounds without launching anything between replays
+        self.history = history
+        self.rounds = torch.zeros((), dtype=torch.int64, device="cuda")
+        self.hist_emit = torch.zeros((max(history, 1), L, depth + 1), dtype=torch.int32, device="cuda")
+        self.hist_n = torch.zeros((max(history, 1), L), dtype=torch.int32, device="cuda")
         self.tok = torch.zeros(L, dtype=torch.int32, device="cuda")
         self.h = torch.zeros((L, 1024), dtype=torch.bfloat16, device="cuda")
         self.emit = torch.zeros((L, depth + 1), dtype=torch.int32, device="cuda")
@@ -536,11 +542,25 @@ class MtpRoundGraph:
             self.tok.copy_(self.emit.gather(1, (self.n_emit - 1).long()[:, None])[:, 0])
             self.h.copy_(h_next)
             self.emitted_total += self.n_emit.sum()
-        # capture ran no kernel but advanced the host-side bounds once, which accounts for the first replay
+            if history > 0:
+                slot = (self.rounds % history).view(1)
+                self.hist_emit.index_copy_(0, slot, self.emit.unsqueeze(0))
+                self.hist_n.index_copy_(0, slot, self.n_emit.unsqueeze(0))
+            self.rounds += 1
+        # capture ran no kernel but advanced the host-side bounds once: take that back, every replay reports itself
+        state.note_advance(-(depth + 1))
+        mtp.note_advance(-depth)
 
     def replay(self):
-        if self.replays > 0:
-            self.state.note_advance(self.depth + 1)
-            self.mtp.note_advance(self.depth)
+        self.state.note_advance(self.depth + 1)
+        self.mtp.note_advance(self.depth)
         self.replays += 1
         self.graph.replay()
+
+    def last_rounds(self, n: int):
+        """Verdicts of the last n <= history replays, oldest first: (emit [n, lanes, depth + 1], n_emit [n, lanes]) on
+        the host.  Synchronises."""
+        assert 0 < n <= self.history
+        done = int(self.rounds)
+        idx = torch.tensor([(done - n + i) % self.history for i in range(n)], device="cuda")
+        return self.hist_emit[idx].cpu(), self.hist_n[idx].cpu()

@@ -129,15 +129,19 @@ class DepthTracker:
 
 
 def speculate(engine, state, mtp, first_token, h_norm, budget: int, start_k: int = 2, readback_every: int = 8,
-              tracker: DepthTracker | None = None):
+              tracker: DepthTracker | None = None, graphs: bool = False):
     """Greedy generation of at least `budget` tokens per lane after a prefill, with adaptive depth.
 
     `first_token` [lanes] and `h_norm` [lanes, 1024] are what `engine.prefill(..., want_normed=True)`
     returned.  Returns (tokens: list of per-lane lists, tracker, plain_steps).  Rounds are chained
     on the device; the emitted counts are read back every `readback_every` rounds.  The draft cache
     of `mtp` must hold one row per drafted token (depth x rounds), the state's context the prompt
-    plus (depth + 1) x rounds.
+    plus (depth + 1) x rounds.  With `graphs=True` the rounds between two readbacks are replays of one captured
+    CUDA graph per depth (`engine.MtpRoundGraph` with a verdict ring of `readback_every` slots): same tokens,
+    same decisions, nothing launched between the rounds.
     """
+    if graphs:
+        return _speculate_graphs(engine, state, mtp, first_token, h_norm, budget, start_k, readback_every, tracker)
     lanes = state.lanes
     tr = tracker or DepthTracker(start_k)
     out = [[int(x)] for x in first_token.tolist()]
@@ -179,6 +183,59 @@ def speculate(engine, state, mtp, first_token, h_norm, budget: int, start_k: int
         t = emit.gather(1, (n_emit - 1).long()[:, None])[:, 0].int().contiguous()
         pending.append((k, emit, n_emit))
         if len(pending) >= readback_every:
+            flush()
+    flush()
+    return out, tr, plain_steps
+
+
+def _speculate_graphs(engine, state, mtp, first_token, h_norm, budget, start_k, readback_every, tracker):
+    from .engine import MtpRoundGraph
+
+    lanes = state.lanes
+    tr = tracker or DepthTracker(start_k)
+    out = [[int(x)] for x in first_token.tolist()]
+    t, h = first_token.clone(), h_norm.clone()
+    plain_steps = 0
+    by_depth = {}                                  # depth -> captured round
+    cur = None                                     # the graph whose buffers hold the live token and row
+    pending = 0
+
+    def flush():
+        nonlocal pending, t, h
+        if cur is None or pending == 0:
+            return
+        em, ne = cur.last_rounds(pending)          # synchronises
+        for r in range(pending):
+            for i in range(lanes):
+                out[i].extend(em[r, i, :int(ne[r, i])].tolist())
+            tr.note(cur.depth, float(ne[r].float().mean()))
+        state.sync_bound()
+        mtp.sync_bound()
+        t, h = cur.tok.clone(), cur.h.clone()
+        pending = 0
+
+    while min(len(o) for o in out) + pending < budget + 1:
+        k = tr.k
+        if k == PLAIN:
+            flush()
+            if min(len(o) for o in out) >= budget + 1:
+                break
+            t = engine.decode_step(state, t)
+            for i, x in enumerate(t.tolist()):
+                out[i].append(int(x))
+            plain_steps += 1
+            continue
+        g = by_depth.get(k)
+        if g is not cur or g is None:
+            flush()                                # the depth only changes at a readback, so nothing is pending here
+            if g is None:
+                g = by_depth[k] = MtpRoundGraph(engine, state, mtp, depth=k, history=readback_every)
+            g.tok.copy_(t)
+            g.h.copy_(h)
+            cur = g
+        cur.replay()
+        pending += 1
+        if pending >= readback_every:
             flush()
     flush()
     return out, tr, plain_steps

@@ -76,7 +76,8 @@ def test_depth_one_start_and_marginal_acceptance(pkg):
 
 
 @pytest.mark.gpu
-def test_adaptive_loop_gives_up_and_stays_lossless(pkg, weights, golden):
+@pytest.mark.parametrize("graphs", [False, True])
+def test_adaptive_loop_gives_up_and_stays_lossless(pkg, weights, golden, graphs):
     pkg.build_lib.build()
     eng = pkg.Engine(weights, max_rows=256)
     lanes, budget = 3, 56
@@ -98,7 +99,7 @@ def test_adaptive_loop_gives_up_and_stays_lossless(pkg, weights, golden):
     ss = eng.allocate_state(lanes, 16 + budget + 24)
     m = eng.mtp_allocate(ss, 40, depth=2)
     t, h = eng.prefill(ss, ids, want_normed=True)
-    out, tr, plain_steps = pkg.mtp_adaptive.speculate(eng, ss, m, t, h, budget, start_k=2, readback_every=8)
+    out, tr, plain_steps = pkg.mtp_adaptive.speculate(eng, ss, m, t, h, budget, start_k=2, readback_every=8, graphs=graphs)
     for i in range(lanes):
         assert len(out[i]) >= budget + 1
         n = min(len(out[i]), plain.shape[0])
