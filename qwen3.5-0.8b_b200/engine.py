@@ -488,12 +488,12 @@ class StepGraph:
         with torch.cuda.graph(self.graph):
             for i in range(steps):
                 engine.decode_step(state, self.buf[i % 2], self.buf[(i + 1) % 2])
-        # capture ran no kernel but advanced the host-side position bound once per captured step,
-        # which accounts for the first replay
+        # capture ran no kernel but advanced the host-side position bound once per captured step: take
+        # that back, every replay reports itself (so a bound tightened between capture and replay stays right)
+        state.note_advance(-steps)
 
     def replay(self):
-        if self.replays > 0:
-            self.state.note_advance(self.n)
+        self.state.note_advance(self.n)
         self.replays += 1
         self.graph.replay()
 
