@@ -21,6 +21,7 @@
 #include <cstdlib>
 
 #include "q35_common.cuh"
+#include "q35_async.cuh"
 
 namespace q35 {
 
@@ -460,7 +461,6 @@ constexpr int V_LD = 136;              // f32 row stride of the right-hand side 
 constexpr size_t kChunkTcSmem = (size_t)128 * S_LD * 4 + (size_t)C * V_LD * 4 +
                                 2 * (size_t)C * KQ_LD * 2 + 3 * (size_t)C * T_LD * 4 + 8 * C * 4 + 2 * C * 4;
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void ldsm4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -588,9 +588,9 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
             const uint16_t* pr = pr0 + (size_t)(r < valid ? r : 0) * kGdnProjN + h * 128 + cc * 8;
             const uint32_t n = r < valid ? 16u : 0u;                // 0 bytes read = 16 bytes of zeros written
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
-                         ::"r"(smem_addr(Q_s + r * KQ_LD + cc * 8)), "l"(pr), "r"(n) : "memory");
+                         ::"r"(smem_u32(Q_s + r * KQ_LD + cc * 8)), "l"(pr), "r"(n) : "memory");
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n"
-                         ::"r"(smem_addr(K_s + r * KQ_LD + cc * 8)), "l"(pr + 2048), "r"(n) : "memory");
+                         ::"r"(smem_u32(K_s + r * KQ_LD + cc * 8)), "l"(pr + 2048), "r"(n) : "memory");
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
         uint4 vraw[4];                               // this thread's v pieces, used by the right-hand sides
@@ -609,7 +609,7 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         if (ck == 0) {
             for (int i = tid; i < 128 * 32; i += 256)
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n"
-                             ::"r"(smem_addr(S_s + (i >> 5) * S_LD + (i & 31) * 4)), "l"(S_g + 4 * i) : "memory");
+                             ::"r"(smem_u32(S_s + (i >> 5) * S_LD + (i & 31) * 4)), "l"(S_g + 4 * i) : "memory");
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
         if (tid < C) {
@@ -690,8 +690,8 @@ gdn_chunk_tc_kernel(const uint16_t* __restrict__ proj, const uint16_t* __restric
         {
             const int mt = warp < 4 ? warp : 7 - warp, m0 = 16 * mt;    // work grows with mt: a scheduler's two warps get mt and 3 - mt
             const bool is_p = warp >= 4;
-            const uint32_t a_base = smem_addr(is_p ? Q_s : K_s) + (uint32_t)((m0 + (ln & 15)) * KQ_LD + (ln >> 4) * 8) * 2u;
-            const uint32_t b_base = smem_addr(K_s) + (uint32_t)(((ln & 7) + (ln >> 4) * 8) * KQ_LD + ((ln >> 3) & 1) * 8) * 2u;
+            const uint32_t a_base = smem_u32(is_p ? Q_s : K_s) + (uint32_t)((m0 + (ln & 15)) * KQ_LD + (ln >> 4) * 8) * 2u;
+            const uint32_t b_base = smem_u32(K_s) + (uint32_t)(((ln & 7) + (ln >> 4) * 8) * KQ_LD + ((ln >> 3) & 1) * 8) * 2u;
             float acc[4][2][4];
 #pragma unroll
             for (int np = 0; np < 4; ++np)
