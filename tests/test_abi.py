@@ -68,6 +68,8 @@ def test_bad_arguments_are_refused_without_cuda(lib):
     assert b"q35_mtp_verify_k" in lib.q35_last_error()
     assert lib.q35_state_sync_bound(null, null) == 1
     assert lib.q35_mtp_state_sync_bound(null, null) == 1
+    assert lib.q35_state_note_advance(null, 1) == 1
+    assert lib.q35_mtp_state_note_advance(null, 1) == 1
     assert lib.q35_lm_head_argmax_static(null, null, 248320, 1, null, null) == 1
 
 
