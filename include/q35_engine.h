@@ -23,7 +23,9 @@ extern "C" {
 
 enum {
     Q35_OK = 0,
-    Q35_ERR_ARG = 1,       /* null / misaligned pointer, size out of range, token id out of range   */
+    Q35_ERR_ARG = 1,       /* null / misaligned pointer, size out of range.  Token ids live in device
+                              memory and are not read by the host: the embedding gather clamps them
+                              to [0, vocab); a host-buffer caller validates them before the copy     */
     Q35_ERR_CUDA = 2,      /* a CUDA runtime call failed                                             */
     Q35_ERR_CAPACITY = 3,  /* lanes, rows or context beyond what the object was created for          */
     Q35_ERR_STATE = 4      /* call order violated (e.g. MTP verify without an MTP state)             */
@@ -41,8 +43,7 @@ enum {
 enum {
     Q35_FAM_GLUE = 0, Q35_FAM_IN_PROJ = 1, Q35_FAM_GDN = 2, Q35_FAM_ATTN = 3, Q35_FAM_OUT_PROJ = 4,
     Q35_FAM_MLP_GATEUP = 5, Q35_FAM_MLP_DOWN = 6, Q35_FAM_HEAD = 7,
-    Q35_FAM_STEP = 8,      /* the one persistent kernel that runs a whole step at <= 16 lanes */
-    Q35_FAMILIES = 9
+    Q35_FAMILIES = 8
 };
 
 typedef struct q35_engine q35_engine;
@@ -112,9 +113,11 @@ typedef struct {
     long long lane_state_bytes;   /* per lane: GDN state read+write + conv window (f32 census) */
     long long kv_bytes_per_pos;   /* 12,288                                                 */
     long long flops_per_row;      /* matmul flops per token                                 */
-    int launches_decode;          /* kernels one q35_decode_step enqueues (more than 16 lanes) */
-    int launches_decode_few_lanes;/* the same at <= 16 lanes: equal to launches_decode unless the
-                                     one-kernel step was switched on (Q35_SMALL_STEP=1)              */
+    int launches_decode;          /* kernels one q35_decode_step enqueues for a body beyond the fused row
+                                     limit: embedding + 24 x 7 + head, argmax, position advance          */
+    int launches_decode_few_lanes;/* the same for a body of at most 16 rows: 24 x 5 blocks, the residual
+                                     add + norm folded into the projections; equal to launches_decode
+                                     when Q35_FUSE=0                                                     */
 } q35_census;
 
 const char* q35_last_error(void);
@@ -132,18 +135,21 @@ int q35_step_census(const q35_engine* e, q35_census* out);
  * reference has no device-side waits; its nearest relative is the post-step
  * RequestState::check_invariants (engine/state.h:99). */
 int q35_engine_status(q35_engine* e, int* status_host);
+/* Clears the status word (enqueued on `stream`).  Once a kernel has raised it every later kernel of the
+ * engine returns without work, so a caller that has dealt with the failure (state reset, lanes
+ * re-prefilled) calls this to go on with the same engine.  The reference has no counterpart (no
+ * device-side waits). */
+int q35_engine_clear_status(q35_engine* e, void* stream);
+/* Kernels enqueued through this engine since its creation (host counter; a kernel captured into a
+ * CUDA graph counts once, at capture).  The launch census of the reference's stage_clock
+ * (engine/decode_step.cpp:39-52) as one number. */
+int q35_engine_launch_count(q35_engine* e, long long* count_host);
 /* Per-family kernel timing with CUDA events on the launching stream (replaces the reference's
  * stage_clock, engine/stage_clock.h:59-67).  Between begin and end every kernel of every body is
  * bracketed by an event pair; end synchronises on the last event and returns the summed
  * milliseconds and launch counts per family (arrays of Q35_FAMILIES, host memory). */
 int q35_profile_begin(q35_engine* e);
 int q35_profile_end(q35_engine* e, double* ms_by_family, long long* launches_by_family);
-/* Phase clock of the last few-lane step taken while profiling was on (the persistent kernel has no
- * launches to bracket): trace_host[2k] / [2k+1] = nanosecond timer of CTA 0 when it left barrier k /
- * reached barrier k+1 (k = 0 is kernel entry); n <= 320 values.  Synchronises the device.  Replaces
- * the per-family segments of the reference's stage_clock (engine/stage_clock.h:59-67). */
-int q35_small_step_trace(q35_engine* e, unsigned long long* trace_host, int n);
-
 /* ---- per-lane state tuple ----------------------------------------------------------------------
  * Replaces allocate_state / free_state / RequestState::reset / state_sizes
  * (engine/state.h:83-120) for `lanes` requests of up to `max_ctx` positions each. */
@@ -155,8 +161,12 @@ int q35_state_reset(q35_state* s, void* stream);
  * positions_out [lanes] (device). */
 int q35_state_positions(q35_state* s, int* positions_out, void* stream);
 /* The host keeps an upper bound of the lanes' positions for its capacity checks
- * (RequestState::check_invariants, engine/state.h:99).  A caller that replays a captured CUDA graph
- * of the step reports the replayed steps here; the captured call itself already counted once. */
+ * (RequestState::check_invariants, engine/state.h:99); every body call adds its tokens to it.  A
+ * captured CUDA graph runs no host code when replayed, so its caller reports each replay's steps
+ * here.  n may be negative: the capture of a graph ran the body calls once on the host without
+ * running a kernel, and the caller takes those steps back (n = -steps) so that every replay,
+ * the first included, reports itself.  The bound never goes below 0 or beyond max_ctx
+ * (Q35_ERR_CAPACITY). */
 int q35_state_note_advance(q35_state* s, int n);
 /* Speculative rounds advance a lane by 1..k+1 positions on the device; the host's bound moves by the
  * maximum.  This reads the true positions back (stream synchronisation) and tightens the bound. */
@@ -195,7 +205,8 @@ int q35_mtp_state_reset(q35_mtp_state* m, void* stream);
  * everything drops its rows on the device: read the true lengths back and tighten the bound. */
 int q35_mtp_state_sync_bound(q35_mtp_state* m, void* stream);
 /* Host bound of the draft cache for a caller that replays a captured CUDA graph of a round: n rows
- * per replay (the capture itself counted once); Q35_ERR_CAPACITY when the cache would overflow.  The
+ * per replay; negative n takes back what the capture itself added (see q35_state_note_advance);
+ * Q35_ERR_CAPACITY when the cache would overflow or the bound would go below 0.  The
  * reference reads its verdict words back every round (engine/mtp_verify.h:117-125) and needs no
  * such bound; rounds chained on the device do. */
 int q35_mtp_state_note_advance(q35_mtp_state* m, int n);
@@ -212,6 +223,14 @@ int q35_mtp_draft(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const
  * needs. */
 int q35_mtp_verify(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur, const int* cand,
                    int* emit, int* n_emit, uint16_t* h_next, void* stream);
+/* A verify of depth k is refused with Q35_ERR_STATE unless k drafts were enqueued on this MTP state
+ * since its last verify or reset: a rejecting round drops k rows from the draft cache. */
+/* q35_mtp_draft with the block's intermediate rows copied out (each optional): u [lanes][1024] = the
+ * fc output, xd [lanes][1024] = the block's final-norm rows, logits_f32 [lanes][vocab]
+ * (speccheck/mtp.py:57-83, taps `mtp.u`, `mtp.x_d`, `mtp.logits_last`). */
+int q35_mtp_draft_taps(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                       const int* pos, int* proposal, uint16_t* u, uint16_t* xd, float* logits_f32,
+                       void* stream);
 /* Depth-k rounds (k = 1 or 2; 2 is the reference's shipped round, engine/mtp_accept.h:87-140).
  * q35_mtp_state_reserve_depth allocates the k shadow state buffers a depth-k round checkpoints into
  * (one per body row except the last, engine/mtp_accept.h:135-140) and the chaining scratch.
@@ -238,6 +257,23 @@ int q35_op_add_norm(const uint16_t* x, const uint16_t* delta, const uint16_t* w,
  * K in {1024, 2048, 3584}; N a multiple of 8. */
 int q35_op_linear(const uint16_t* x, const uint16_t* W, uint16_t* out, int rows, int N, int K,
                   void* stream);
+/* The fused residual stream of bodies of at most 16 rows, as two stages (the reference's pairing of
+ * residual adds with norms, engine/decode_step.h:9-15, prototype/glue/glue_kernels.h:84-128).
+ * q35_op_linear_resid: resid [rows][1024] <- bf16(resid + bf16(x [rows][K] . W[1024][K]^T)) in place,
+ * K in {2048, 3584}.  q35_op_linear_norm: out [rows][N] = bf16(N(resid; nw) . W[N][1024]^T) with the
+ * zero-centred RMSNorm applied while the rows are staged (swiglu != 0: W is the row-interleaved
+ * gate/up matrix and out is [rows][N/2]).  More than 16 rows: Q35_ERR_CAPACITY. */
+int q35_op_linear_resid(q35_engine* e, const uint16_t* x, const uint16_t* W, uint16_t* resid, int rows,
+                        int K, void* stream);
+int q35_op_linear_norm(q35_engine* e, const uint16_t* resid, const uint16_t* nw, const uint16_t* W,
+                       uint16_t* out, int rows, int N, int swiglu, void* stream);
+/* One decoder block in isolation (Forward._layer, speccheck/specimpl.py:426-451; the per-layer
+ * teacher-forcing taps L{l}.s_in -> L{l}.s_out): x_in [lanes*T][1024] = the block's input residual
+ * rows, x_out = its output rows.  Reads the lanes' state at their current positions and updates that
+ * block's part of it; does NOT advance the positions.  fused: 1 / 0 force the fused / unfused
+ * residual stream, -1 = what a body of this size takes. */
+int q35_op_layer(q35_engine* e, q35_state* s, int layer, const uint16_t* x_in, uint16_t* x_out, int T,
+                 int fused, void* stream);
 /* mlp_gateup (engine/kernels.h:363-374): act [rows][3584] from x [rows][1024]; Wgu is the
  * row-interleaved matrix q35_pack_gate_up writes ([7168][1024]: row 2f = gate f, 2f+1 = up f). */
 int q35_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* Wgu, void* stream);

@@ -9,7 +9,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "libq35_b200.so"
-SOURCES = ["q35_engine.cu", "q35_gemm.cu", "q35_gemm_tc.cu", "q35_glue.cu", "q35_gdn.cu", "q35_gdn_chunk.cu", "q35_attn.cu", "q35_small_step.cu"]
+SOURCES = ["q35_engine.cu", "q35_gemm.cu", "q35_gemm_tc.cu", "q35_glue.cu", "q35_gdn.cu", "q35_gdn_chunk.cu", "q35_attn.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

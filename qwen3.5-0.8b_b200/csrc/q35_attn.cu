@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(64) attn_append_kernel(AttnParams p) {
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int lane_id = row / p.T, t = row % p.T;
     const int slot = p.slot[lane_id] + t;
-    if (slot >= p.pages_per_lane * kKvPage) return;
+    if (slot < 0 || slot >= p.pages_per_lane * kKvPage) return;
     const int* table = p.page_table + (size_t)lane_id * p.table_lane_stride;
     append_kv(p, p.proj + (size_t)row * kAttnProjN, table, kvh, slot, p.rope_pos[lane_id] + t,
               threadIdx.x >> 5, threadIdx.x & 31);
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256, 2) attn_decode_kernel(AttnParams p, int c
     const int cap = p.pages_per_lane * kKvPage;
     int slot = p.slot[lane_id] + t;
     const int rope_pos = p.rope_pos[lane_id] + t;
-    const bool in_cap = slot < cap && slot < ctx_pad;
+    const bool in_cap = slot >= 0 && slot < cap && slot < ctx_pad;   // a negative slot (a state driven out of order) is never indexed
     if (!in_cap) slot = (cap < ctx_pad ? cap : ctx_pad) - 1;   // never index past the cache; host checks capacity
     const int n_ctx = slot + 1;
     const int* table = p.page_table + (size_t)lane_id * p.table_lane_stride;
@@ -266,7 +266,7 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
     const int cap = p.pages_per_lane * kKvPage;
     int slot = p.slot[lane_id] + tt;
     const int rope_pos = p.rope_pos[lane_id] + tt;
-    const bool in_cap = slot < cap && slot < ctx_pad;
+    const bool in_cap = slot >= 0 && slot < cap && slot < ctx_pad;   // a negative slot (a state driven out of order) is never indexed
     if (!in_cap) slot = (cap < ctx_pad ? cap : ctx_pad) - 1;
     const int n_ctx = slot + 1;
     const int P = (n_ctx + kKvPage - 1) / kKvPage;          // pages (tiles) per pass
@@ -499,7 +499,7 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int lpad, int cs, const __grid_co
     const int cap = p.pages_per_lane * kKvPage;
     int slot = p.slot[lane_id] + tt;
     const int rope_pos = p.rope_pos[lane_id] + tt;
-    const bool in_cap = slot < cap && slot < ctx_pad;
+    const bool in_cap = slot >= 0 && slot < cap && slot < ctx_pad;   // a negative slot (a state driven out of order) is never indexed
     if (!in_cap) slot = (cap < ctx_pad ? cap : ctx_pad) - 1;
     const int n_ctx = slot + 1;
     const int P = (n_ctx + kKvPage - 1) / kKvPage;                       // pages of the whole context
@@ -756,7 +756,7 @@ attn_prefill_kernel(AttnParams p, const __grid_constant__ CUtensorMap kmap, cons
     const int tid = threadIdx.x, warp = tid >> 5, ln = tid & 31;
     const int g = ln >> 2, t = ln & 3;
     const int cap = p.pages_per_lane * kKvPage;
-    const int slot0 = p.slot[lane_id];                      // position of the body's first row
+    const int slot0 = p.slot[lane_id] > 0 ? p.slot[lane_id] : 0;   // position of the body's first row (never negative)
     const int rope0 = p.rope_pos[lane_id];
     const int rows_here = (p.T - t0) < kPfRows ? (p.T - t0) : kPfRows;
     int last = slot0 + t0 + rows_here - 1;                  // last key position any row of the block sees

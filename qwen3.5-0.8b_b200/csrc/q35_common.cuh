@@ -57,7 +57,7 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// ---- attention head helpers (shared by q35_attn.cu and q35_small_step.cu) ------------------------
+// ---- attention head helpers ----------------------------------------------------------------------
 constexpr int kHeadDimC = 256;
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[0] = lo_bf(v.x); f[1] = hi_bf(v.x); f[2] = lo_bf(v.y); f[3] = hi_bf(v.y);
@@ -134,7 +134,30 @@ __device__ __forceinline__ void prefetch_tensormap(const void* map) {
 }
 
 bool pdl_enabled();            // Q35_PDL=1/0 forces; unset: on for bodies of few rows (pdl_set_rows)
-void pdl_set_rows(int rows);   // the engine announces the row count of the body it is about to launch
+void pdl_set_rows(int rows);   // the engine announces the row count of the body it is about to launch (per host thread)
+
+// ---- per-device facts ------------------------------------------------------------------------------
+// Kernel attributes and the SM count belong to a device, not to the process: the flags and counts are
+// kept per device ordinal (several engines on several devices may live in one process).
+constexpr int kMaxDevices = 64;
+int sm_count();                // multiprocessors of the current device
+inline int current_device_slot() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+}
+// opt a kernel in to `smem` bytes of dynamic shared memory, once per device
+template <typename Kern>
+inline cudaError_t opt_in_smem(Kern kern, size_t smem, bool (&done)[kMaxDevices]) {
+    const int dev = current_device_slot();
+    if (dev < 0) return cudaErrorInvalidDevice;
+    if (!done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        done[dev] = true;
+    }
+    return cudaSuccess;
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
@@ -153,7 +176,7 @@ inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_
 }
 
 // ---- launcher declarations (defined one per .cu file) -----------------------------------------
-enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2 };
+enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_PARTIAL = 3, EPI_RESID = 4 };
 
 // out[rows][N] (or act / partial argmax) = x[rows][K] . W[N][K]^T, picks the few-row or tiled form.
 // EPI_SWIGLU: W rows interleaved (2f gate, 2f+1 up), out [rows][N/2].
@@ -173,6 +196,16 @@ cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* 
 cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
                              ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st);
 int linear_argmax_parts(int rows, int N);
+// Fused residual stream of bodies of at most kFusedMaxRows rows (the weight-streaming kernels): the
+// output / down projection adds its result to the residual rows in place; the next in-projection /
+// gate-up projection applies the RMSNorm (weights nw) while it stages those rows - every CTA holds all
+// rows, so it takes their sums of squares from its own registers.  No add + norm kernel runs in between.
+// pf / pf_bytes (optional): weights of a later kernel of the body, pulled into L2 by this one.
+constexpr int kFusedMaxRows = 16;
+cudaError_t launch_linear_resid_rows(const uint16_t* x, const uint16_t* W, uint16_t* resid, int rows, int K,
+                                     const void* pf, size_t pf_bytes, cudaStream_t st);
+cudaError_t launch_linear_norm_rows(const uint16_t* resid, const uint16_t* nw, const uint16_t* W, void* out, int rows,
+                                    int N, int epi, const void* pf, size_t pf_bytes, cudaStream_t st);
 cudaError_t launch_argmax_final(const ArgMax* partials, int n_parts, int rows, int* tokens,
                                 float* top_logit, cudaStream_t st);
 cudaError_t launch_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* out,
@@ -247,39 +280,6 @@ constexpr int kTensorMapBytes = 128;
 bool attn_make_pool_map(void* map_out, const uint16_t* pool, long long n_pages);
 cudaError_t launch_attn(const AttnParams& p, cudaStream_t st);
 cudaError_t attn_init();       // opt in to large dynamic shared memory; call once per device
-
-// ---- one persistent kernel per decode step for <= 16 lanes (q35_small_step.cu) -----------------
-struct SmallLayer {
-    const uint16_t *in_w, *out_w, *gu_w, *down_w, *input_norm, *post_norm;
-    const uint16_t *conv_w, *A_log, *dt_bias, *gdn_norm, *q_norm, *k_norm;
-    int in_n, attn, slot;      // slot: index among the GDN (or attention) layers
-    int pad_;
-};
-struct SmallStepParams {
-    const SmallLayer* layers;  // [24], device memory
-    const uint16_t* embed;
-    const uint16_t* final_norm;
-    int vocab, lanes;
-    const int* in_tok;
-    int* out_tok;
-    float* S;                  // [18][lanes][16][128][128]
-    uint16_t* win;             // [18][lanes][3][6144]
-    uint16_t *kpool, *vpool;
-    const int* table;          // [lanes][6][pages_per_lane]
-    int pages_per_lane;
-    int* pos;
-    const float* inv_freq;
-    uint16_t *resid;           // [2][16][1024]
-    uint16_t *delta, *proj, *mix, *act, *normed;
-    float* attn_part;          // [16][8][pages_per_lane][260]
-    ArgMax* head_part;         // [grid][16]
-    unsigned* bar;             // grid-barrier counter, zeroed before every launch
-    unsigned long long* trace; // optional [2 * 160]: CTA 0's clock when it reaches / leaves each barrier
-    int* status;
-};
-constexpr int kSmallStepMaxLanes = 16;
-constexpr int kSmallStepLaunches = 1;      // kernels per step (plus a 4-byte memset of the barrier counter)
-cudaError_t launch_small_step(const SmallStepParams& p, cudaStream_t st);
 
 // state tuple <-> reference layouts
 cudaError_t launch_window_export(const uint16_t* win, float* out, cudaStream_t st);   // [3][6144]x18 handled by caller loop

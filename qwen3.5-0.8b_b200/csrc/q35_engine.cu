@@ -75,17 +75,13 @@ struct q35_engine {
     int *tok2 = nullptr, *tgt = nullptr;     // [max_rows] token scratch
     float* inv_freq = nullptr;
     int* dev_status = nullptr;               // raised by a kernel whose bounded wait expired
-    // few-lane persistent step kernel: device copy of the layer table and its scratch
-    SmallLayer* small_layers = nullptr;
-    uint16_t* small_resid = nullptr;         // [2][16][1024]
-    ArgMax* small_head_part = nullptr;       // [1024][16]
-    unsigned* small_bar = nullptr;
-    unsigned long long* small_trace = nullptr;   // [320] phase clock of the last traced step
     float* split_ws = nullptr;               // [kMaxSplits][kSplitMaxRows][1024] f32 K-split partials
+    bool l2_prefetch = true;                 // Q35_L2PF=0: few-row projections do not pull the next one's weights into L2
+    bool fuse_enabled = true;                // Q35_FUSE=0: every body takes the add + norm kernels
+    long long n_launch = 0;                  // kernels enqueued through this engine (captured ones count once)
     long long weight_bytes = 0;
     std::vector<void*> allocs;
     // optional per-family kernel timing (CUDA events on the launching stream)
-    bool small_step_enabled = false;         // Q35_SMALL_STEP=1: few-lane steps run as ONE persistent kernel (measured slower, so opt-in)
     bool prof_on = false;
     std::vector<cudaEvent_t> prof_events;     // pairs: [2i] before, [2i+1] after
     std::vector<int> prof_family;
@@ -103,7 +99,6 @@ struct q35_state {
     uint16_t *kpool = nullptr, *vpool = nullptr;
     int* table = nullptr;                      // [lanes][6][pages_per_lane]
     int* pos = nullptr;                        // [lanes]
-    float* attn_part = nullptr;                // few-lane step kernel: [16][8][pages_per_lane][260] page partials
     int host_pos_hi = 0;                       // upper bound of any lane's position (host mirror)
     long long n_pages = 0;
     alignas(64) unsigned char kmap[kTensorMapBytes];   // TMA tensor maps of the two pools
@@ -119,6 +114,7 @@ struct q35_mtp_state {
     int* table = nullptr;                      // [lanes][pages_per_lane]
     int* n = nullptr;                          // [lanes] rows in the draft cache
     int host_n_hi = 0;
+    int drafts_pending = 0;                    // drafts enqueued since the last verify or reset (a verify of depth k needs k)
     int depth = 1;                             // candidates per round the shadow buffers allow
     uint16_t* h_tmp = nullptr;                 // [lanes][1024] a draft's output hidden, input of the next
     int* pos_tmp = nullptr;                    // [lanes]
@@ -190,7 +186,8 @@ __global__ void mtp_verdict_kernel(const int* __restrict__ cand, const int* __re
             int b = sel[lane_id] + 1 + n;
             if (b > k) b -= k + 1;
             sel[lane_id] = b;
-            mtp_n[lane_id] -= k;
+            const int left = mtp_n[lane_id] - k;      // never below an empty cache, whatever order the host called in
+            mtp_n[lane_id] = left > 0 ? left : 0;
         }
     }
     const uint4* src = reinterpret_cast<const uint4*>(normed + ((size_t)lane_id * (k + 1) + n) * kHidden);
@@ -249,7 +246,14 @@ static cudaError_t prof_end(q35_engine* e, cudaStream_t st) {
     do {                                                      \
         if (e->prof_on) CK(prof_begin(e, family, st));        \
         CK(call);                                             \
+        e->n_launch += 1;                                     \
         if (e->prof_on) CK(prof_end(e, st));                  \
+    } while (0)
+// a kernel outside the families (token plumbing): counted, not timed
+#define LAUNCH_PLAIN(call)                                    \
+    do {                                                      \
+        CK(call);                                             \
+        e->n_launch += 1;                                     \
     } while (0)
 
 extern "C" int q35_profile_begin(q35_engine* e) {
@@ -332,8 +336,10 @@ static int pack_layer(q35_engine* e, const q35_layer_weights& w, bool attn, Pack
 static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights* w, cudaStream_t st) {
     e->cfg = *cfg;
     {
-        const char* env = getenv("Q35_SMALL_STEP");
-        e->small_step_enabled = env != nullptr && env[0] == '1';
+        const char* env = getenv("Q35_FUSE");
+        e->fuse_enabled = !(env != nullptr && env[0] == '0');
+        env = getenv("Q35_L2PF");
+        e->l2_prefetch = !(env != nullptr && env[0] == '0');
     }
     e->vocab = cfg->vocab;
     e->max_rows = cfg->max_rows;
@@ -384,24 +390,6 @@ static int engine_build(q35_engine* e, const q35_config* cfg, const q35_weights*
     CK(dev_alloc(e->allocs, &e->split_ws, (size_t)kMaxSplits * kSplitMaxRows * kHidden));
     CK(dev_alloc(e->allocs, &e->dev_status, (size_t)4));
     CK(cudaMemsetAsync(e->dev_status, 0, 4 * sizeof(int), st));
-    {
-        SmallLayer tbl[kLayers];
-        int gs = 0, as = 0;
-        for (int l = 0; l < kLayers; ++l) {
-            const PackedLayer& L = e->layers[l];
-            tbl[l] = SmallLayer{L.in_w, L.out_w, L.gu_w, L.down_w, L.input_norm, L.post_norm, L.conv_w, L.A_log,
-                                L.dt_bias, L.gdn_norm, L.q_norm, L.k_norm, L.in_n, L.attn ? 1 : 0,
-                                L.attn ? as++ : gs++, 0};
-        }
-        CK(dev_alloc(e->allocs, &e->small_layers, (size_t)kLayers));
-        CK(cudaMemcpyAsync(e->small_layers, tbl, sizeof(tbl), cudaMemcpyHostToDevice, st));
-        CK(cudaStreamSynchronize(st));          // tbl lives on this stack frame
-        CK(dev_alloc(e->allocs, &e->small_resid, (size_t)2 * 16 * kHidden));
-        CK(dev_alloc(e->allocs, &e->small_head_part, (size_t)1024 * 16));
-        CK(dev_alloc(e->allocs, &e->small_bar, (size_t)4));
-        CK(dev_alloc(e->allocs, &e->small_trace, (size_t)320));
-        CK(cudaMemsetAsync(e->small_trace, 0, 320 * sizeof(unsigned long long), st));
-    }
     CK(cudaMemcpyAsync(e->inv_freq, e->cfg.rope_inv_freq, 32 * sizeof(float), cudaMemcpyHostToDevice, st));
     CK(cudaStreamSynchronize(st));   // the host-side config copy above must not outlive `cfg`
     return Q35_OK;
@@ -438,12 +426,6 @@ extern "C" int q35_engine_status(q35_engine* e, int* status_host) {
     return Q35_OK;
 }
 
-extern "C" int q35_small_step_trace(q35_engine* e, unsigned long long* trace_host, int n) {
-    REQUIRE(e && trace_host && n >= 1 && n <= 320, Q35_ERR_ARG, "q35_small_step_trace: bad argument");
-    CK(cudaMemcpy(trace_host, e->small_trace, n * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-    return Q35_OK;
-}
-
 extern "C" int q35_step_census(const q35_engine* e, q35_census* out) {
     REQUIRE(e && out, Q35_ERR_ARG, "q35_step_census: null argument");
     out->weight_bytes = e->weight_bytes;
@@ -454,8 +436,8 @@ extern "C" int q35_step_census(const q35_engine* e, q35_census* out) {
         params += ((long long)e->layers[l].in_n + 2048 + 3LL * kFF) * kHidden;
     params += (long long)e->vocab * kHidden;
     out->flops_per_row = 2 * params;
-    out->launches_decode = 1 + kLayers * 7 + 3;
-    out->launches_decode_few_lanes = e->small_step_enabled ? kSmallStepLaunches : out->launches_decode;
+    out->launches_decode = 1 + kLayers * 7 + 3;                                  // bodies beyond the fused row limit
+    out->launches_decode_few_lanes = e->fuse_enabled ? 1 + kLayers * 5 + 1 + 3 : out->launches_decode;
     return Q35_OK;
 }
 
@@ -507,8 +489,6 @@ extern "C" int q35_state_create(q35_engine* e, int lanes, int max_ctx, q35_state
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->vpool, n_pages * kPageElems);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->table, n_pages);
     if (ce == cudaSuccess) ce = dev_alloc(s->allocs, &s->pos, (size_t)lanes);
-    if (ce == cudaSuccess && lanes <= kSmallStepMaxLanes)
-        ce = dev_alloc(s->allocs, &s->attn_part, (size_t)16 * kQHeads * s->pages_per_lane * 260);
     s->n_pages = (long long)n_pages;
     if (ce == cudaSuccess && (!attn_make_pool_map(s->kmap, s->kpool, s->n_pages) ||
                               !attn_make_pool_map(s->vmap, s->vpool, s->n_pages)))
@@ -645,71 +625,109 @@ extern "C" int q35_state_import_lane(q35_state* s, int lane, const float* gdn_st
 // ------------------------------------------------------------------------------------------------
 // the body: `T` tokens per lane through the 24 blocks (T = 1 is the decode step)
 // ------------------------------------------------------------------------------------------------
+// Whether a body of `rows` rows takes the fused residual stream: the output / down projections add
+// into the residual rows in place, the next projection applies the RMSNorm while it stages its rows,
+// and the 48 add + norm kernels of a body do not run.
+static bool body_fused(const q35_engine* e, int rows) { return e->fuse_enabled && rows <= kFusedMaxRows; }
+
+// One block l over `rows` = lanes x T rows.  On entry the residual rows are in e->resid; the normed
+// rows the in-projection reads are in e->normed when `in_from_normed`, else (fused stream) they are
+// formed from e->resid while the projection stages them.  On exit e->resid holds the block's output
+// rows; in the unfused form e->normed also holds them normed with `next_norm`.
+static int run_layer(q35_engine* e, q35_state* s, int l, int T, int checkpoint, bool fused, bool in_from_normed,
+                     const uint16_t* next_norm, const void* next_w, size_t next_w_bytes, cudaStream_t st) {
+    const int rows = s->lanes * T;
+    const PackedLayer& L = e->layers[l];
+    // weights a projection pulls into L2 for the projection after it (few-row bodies only)
+    const bool pf = e->l2_prefetch && fused;
+    const size_t out_bytes = (size_t)kHidden * 2048 * 2, gu_bytes = (size_t)2 * kFF * kHidden * 2, down_bytes = (size_t)kHidden * kFF * 2;
+    int gslot = 0, aslot = 0;
+    for (int i = 0; i < l; ++i) (is_attn_layer(i) ? aslot : gslot) += 1;
+    if (in_from_normed)
+        LAUNCH(Q35_FAM_IN_PROJ, launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+    else
+        LAUNCH(Q35_FAM_IN_PROJ, launch_linear_norm_rows(e->resid, L.input_norm, L.in_w, e->proj, rows, L.in_n, EPI_PLAIN,
+                                                        pf ? L.out_w : nullptr, out_bytes, st));
+    if (L.attn) {
+        AttnParams ap{};
+        ap.proj = e->proj; ap.q_norm = L.q_norm; ap.k_norm = L.k_norm;
+        ap.kpool = s->kpool; ap.vpool = s->vpool;
+        ap.page_table = s->table + (size_t)aslot * s->pages_per_lane;
+        ap.pages_per_lane = s->pages_per_lane;
+        ap.table_lane_stride = (long long)kAttnLayers * s->pages_per_lane;
+        ap.slot = s->pos; ap.rope_pos = s->pos; ap.inv_freq = e->inv_freq;
+        ap.out = e->mix; ap.lanes = s->lanes; ap.T = T; ap.max_ctx = s->max_ctx;
+        ap.n_pages = s->n_pages; ap.kmap = s->kmap; ap.vmap = s->vmap; ap.status = e->dev_status;
+        LAUNCH(Q35_FAM_ATTN, launch_attn(ap, st));
+    } else {
+        GdnParams gp{};
+        gp.proj = e->proj; gp.conv_w = L.conv_w; gp.A_log = L.A_log; gp.dt_bias = L.dt_bias;
+        gp.norm_w = L.gdn_norm;
+        const size_t so = (size_t)gslot * s->lanes * kGdnHeads * kDk * kDv;
+        const size_t wo = (size_t)gslot * s->lanes * 3 * kConvCh;
+        for (int b = 0; b < kStateBufs; ++b) {
+            gp.S[b] = s->S[b] ? s->S[b] + so : nullptr;
+            gp.win[b] = s->win[b] ? s->win[b] + wo : nullptr;
+        }
+        gp.sel = s->sel; gp.y = e->mix; gp.lanes = s->lanes; gp.T = T; gp.checkpoint = checkpoint;
+        gp.status = e->dev_status;
+        if (!checkpoint && T >= kGdnChunkMinT)
+            LAUNCH(Q35_FAM_GDN, launch_gdn_chunked(gp, st));
+        else
+            LAUNCH(Q35_FAM_GDN, launch_gdn_step(gp, st));
+    }
+    if (fused) {
+        LAUNCH(Q35_FAM_OUT_PROJ, launch_linear_resid_rows(e->mix, L.out_w, e->resid, rows, 2048, pf ? L.gu_w : nullptr, gu_bytes, st));
+        LAUNCH(Q35_FAM_MLP_GATEUP, launch_linear_norm_rows(e->resid, L.post_norm, L.gu_w, e->act, rows, 2 * kFF, EPI_SWIGLU,
+                                                           pf ? L.down_w : nullptr, down_bytes, st));
+        LAUNCH(Q35_FAM_MLP_DOWN, launch_linear_resid_rows(e->act, L.down_w, e->resid, rows, kFF, pf ? next_w : nullptr, next_w_bytes, st));
+        return Q35_OK;
+    }
+    {
+        const int sp = linear_tc_splits(rows, kHidden, 2048, kSplitMaxRows);
+        if (sp > 1) {
+            LAUNCH(Q35_FAM_OUT_PROJ, launch_linear_tc_split(e->mix, L.out_w, e->split_ws, rows, kHidden, 2048, sp, e->dev_status, st));
+            LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, L.post_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
+        } else {
+            LAUNCH(Q35_FAM_OUT_PROJ, launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+            LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
+        }
+    }
+    LAUNCH(Q35_FAM_MLP_GATEUP, launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st, e->dev_status));
+    {
+        const int sp = linear_tc_splits(rows, kHidden, kFF, kSplitMaxRows);
+        if (sp > 1) {
+            LAUNCH(Q35_FAM_MLP_DOWN, launch_linear_tc_split(e->act, L.down_w, e->split_ws, rows, kHidden, kFF, sp, e->dev_status, st));
+            LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, next_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
+        } else {
+            LAUNCH(Q35_FAM_MLP_DOWN, launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+            LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, next_norm, e->resid, e->normed, rows, st));
+        }
+    }
+    return Q35_OK;
+}
+
 // ids: compact [lanes*T].  Leaves the final-normed rows in e->normed [lanes*T][1024].
 static int run_body(q35_engine* e, q35_state* s, const int* ids, int T, int checkpoint, cudaStream_t st) {
     const int rows = s->lanes * T;
     REQUIRE(rows <= e->max_rows, Q35_ERR_CAPACITY, "body of %d rows exceeds engine max_rows %d", rows, e->max_rows);
     REQUIRE(s->host_pos_hi + T <= s->max_ctx, Q35_ERR_CAPACITY, "position %d + %d beyond max_ctx %d", s->host_pos_hi, T, s->max_ctx);
     pdl_set_rows(rows);
+    const bool fused = body_fused(e, rows);
     LAUNCH(Q35_FAM_GLUE, launch_add_norm(nullptr, ids, e->embed, e->vocab, nullptr, e->layers[0].input_norm,
                                          e->resid, e->normed, rows, st));
-    int gslot = 0, aslot = 0;
     for (int l = 0; l < kLayers; ++l) {
-        const PackedLayer& L = e->layers[l];
-        LAUNCH(Q35_FAM_IN_PROJ, launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
-        if (L.attn) {
-            AttnParams ap{};
-            ap.proj = e->proj; ap.q_norm = L.q_norm; ap.k_norm = L.k_norm;
-            ap.kpool = s->kpool; ap.vpool = s->vpool;
-            ap.page_table = s->table + (size_t)aslot * s->pages_per_lane;
-            ap.pages_per_lane = s->pages_per_lane;
-            ap.table_lane_stride = (long long)kAttnLayers * s->pages_per_lane;
-            ap.slot = s->pos; ap.rope_pos = s->pos; ap.inv_freq = e->inv_freq;
-            ap.out = e->mix; ap.lanes = s->lanes; ap.T = T; ap.max_ctx = s->max_ctx;
-            ap.n_pages = s->n_pages; ap.kmap = s->kmap; ap.vmap = s->vmap; ap.status = e->dev_status;
-            LAUNCH(Q35_FAM_ATTN, launch_attn(ap, st));
-            ++aslot;
-        } else {
-            GdnParams gp{};
-            gp.proj = e->proj; gp.conv_w = L.conv_w; gp.A_log = L.A_log; gp.dt_bias = L.dt_bias;
-            gp.norm_w = L.gdn_norm;
-            const size_t so = (size_t)gslot * s->lanes * kGdnHeads * kDk * kDv;
-            const size_t wo = (size_t)gslot * s->lanes * 3 * kConvCh;
-            for (int b = 0; b < kStateBufs; ++b) {
-                gp.S[b] = s->S[b] ? s->S[b] + so : nullptr;
-                gp.win[b] = s->win[b] ? s->win[b] + wo : nullptr;
-            }
-            gp.sel = s->sel; gp.y = e->mix; gp.lanes = s->lanes; gp.T = T; gp.checkpoint = checkpoint;
-            gp.status = e->dev_status;
-            if (!checkpoint && T >= kGdnChunkMinT)
-                LAUNCH(Q35_FAM_GDN, launch_gdn_chunked(gp, st));
-            else
-                LAUNCH(Q35_FAM_GDN, launch_gdn_step(gp, st));
-            ++gslot;
-        }
-        {
-            const int sp = linear_tc_splits(rows, kHidden, 2048, kSplitMaxRows);
-            if (sp > 1) {
-                LAUNCH(Q35_FAM_OUT_PROJ, launch_linear_tc_split(e->mix, L.out_w, e->split_ws, rows, kHidden, 2048, sp, e->dev_status, st));
-                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, L.post_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
-            } else {
-                LAUNCH(Q35_FAM_OUT_PROJ, launch_linear(e->mix, L.out_w, e->delta, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
-                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, L.post_norm, e->resid, e->normed, rows, st));
-            }
-        }
-        LAUNCH(Q35_FAM_MLP_GATEUP, launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st, e->dev_status));
         const uint16_t* next_norm = (l + 1 < kLayers) ? e->layers[l + 1].input_norm : e->final_norm;
-        {
-            const int sp = linear_tc_splits(rows, kHidden, kFF, kSplitMaxRows);
-            if (sp > 1) {
-                LAUNCH(Q35_FAM_MLP_DOWN, launch_linear_tc_split(e->act, L.down_w, e->split_ws, rows, kHidden, kFF, sp, e->dev_status, st));
-                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, next_norm, e->resid, e->normed, rows, st, e->split_ws, sp));
-            } else {
-                LAUNCH(Q35_FAM_MLP_DOWN, launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
-                LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, next_norm, e->resid, e->normed, rows, st));
-            }
-        }
+        // what the last projection of the block pulls into L2: the next block's in-projection, or (last block) the
+        // first part of the tied head's table
+        const void* next_w = (l + 1 < kLayers) ? (const void*)e->layers[l + 1].in_w : (const void*)e->embed;
+        size_t next_bytes = (l + 1 < kLayers) ? (size_t)e->layers[l + 1].in_n * kHidden * 2 : (size_t)e->vocab * kHidden * 2;
+        if (next_bytes > ((size_t)48 << 20)) next_bytes = (size_t)48 << 20;
+        int rc = run_layer(e, s, l, T, checkpoint, fused, !fused || l == 0, next_norm, next_w, next_bytes, st);
+        if (rc != Q35_OK) return rc;
     }
+    if (fused)      // the head, the drafts and the caller read plain normed rows
+        LAUNCH(Q35_FAM_GLUE, launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, e->final_norm, nullptr, e->normed, rows, st));
     return Q35_OK;
 }
 
@@ -728,31 +746,12 @@ extern "C" int q35_decode_step(q35_engine* e, q35_state* s, const int* in_tok, i
     REQUIRE(e && s && in_tok && out_tok, Q35_ERR_ARG, "q35_decode_step: null argument");
     REQUIRE(s->e == e, Q35_ERR_STATE, "q35_decode_step: state belongs to another engine");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // Few lanes, no logits wanted, no MTP shadow buffers (a speculative session keeps decode and verify
-    // on the same kernels so that speculation stays bit-lossless): one persistent kernel does the step.
-    if (s->lanes <= kSmallStepMaxLanes && logits_f32 == nullptr && s->sel == nullptr && s->attn_part != nullptr &&
-        e->small_step_enabled) {
-        REQUIRE(s->host_pos_hi + 1 <= s->max_ctx, Q35_ERR_CAPACITY, "position %d + 1 beyond max_ctx %d", s->host_pos_hi, s->max_ctx);
-        SmallStepParams sp{};
-        sp.layers = e->small_layers; sp.embed = e->embed; sp.final_norm = e->final_norm;
-        sp.vocab = e->vocab; sp.lanes = s->lanes; sp.in_tok = in_tok; sp.out_tok = out_tok;
-        sp.S = s->S[0]; sp.win = s->win[0]; sp.kpool = s->kpool; sp.vpool = s->vpool; sp.table = s->table;
-        sp.pages_per_lane = s->pages_per_lane; sp.pos = s->pos; sp.inv_freq = e->inv_freq;
-        sp.resid = e->small_resid; sp.delta = e->delta; sp.proj = e->proj; sp.mix = e->mix; sp.act = e->act;
-        sp.normed = e->normed; sp.attn_part = s->attn_part; sp.head_part = e->small_head_part;
-        sp.bar = e->small_bar; sp.status = e->dev_status;
-        sp.trace = e->prof_on ? e->small_trace : nullptr;
-        LAUNCH(Q35_FAM_STEP, launch_small_step(sp, st));
-        if (normed) CK(copy_rows(normed, e->normed, (size_t)s->lanes * kHidden, st));
-        s->host_pos_hi += 1;
-        return Q35_OK;
-    }
     int rc = run_body(e, s, in_tok, 1, 0, st);
     if (rc != Q35_OK) return rc;
     rc = run_head(e, e->normed, s->lanes, out_tok, logits_f32, st);
     if (rc != Q35_OK) return rc;
     if (normed) CK(copy_rows(normed, e->normed, (size_t)s->lanes * kHidden, st));
-    CK(launch_add_int(s->pos, 1, s->lanes, st));
+    LAUNCH_PLAIN(launch_add_int(s->pos, 1, s->lanes, st));
     s->host_pos_hi += 1;
     return Q35_OK;
 }
@@ -774,7 +773,8 @@ extern "C" int q35_prefill(q35_engine* e, q35_state* s, const int* ids, int T, i
         CK(cudaGetLastError());
         int rc = run_body(e, s, e->tok2, tc, 0, st);
         if (rc != Q35_OK) return rc;
-        CK(launch_add_int(s->pos, tc, s->lanes, st));
+        LAUNCH_PLAIN(launch_add_int(s->pos, tc, s->lanes, st));
+        e->n_launch += 1;                         // the id-slicing kernel ahead of the body
         s->host_pos_hi += tc;
         if (t0 + tc >= T) {
             // last row of every lane -> compact [lanes][1024]
@@ -796,6 +796,7 @@ extern "C" int q35_mtp_state_reset(q35_mtp_state* m, void* stream) {
     REQUIRE(m, Q35_ERR_ARG, "q35_mtp_state_reset: null state");
     CK(cudaMemsetAsync(m->n, 0, m->lanes * sizeof(int), static_cast<cudaStream_t>(stream)));
     m->host_n_hi = 0;
+    m->drafts_pending = 0;
     return Q35_OK;
 }
 
@@ -880,7 +881,8 @@ extern "C" int q35_mtp_state_destroy(q35_mtp_state* m) {
 // One draft pass of the MTP block for every lane (speccheck/mtp.py:57-83): proposal ids, the
 // block's output hidden in e->normed, one row appended to the draft cache.
 static int draft_once(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
-                      const int* pos, int* proposal, cudaStream_t st) {
+                      const int* pos, int* proposal, cudaStream_t st, uint16_t* u_out = nullptr,
+                      float* logits_out = nullptr) {
     const int rows = m->lanes;
     const PackedLayer& L = e->mtp_layer;
     // pair = [ N(E[y]; norm_emb) | N(h; norm_hid) ], written as two 1024-wide halves of [rows][2048]
@@ -891,6 +893,7 @@ static int draft_once(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, c
     CK(cudaMemcpy2DAsync(e->pair + kHidden, 2048 * sizeof(uint16_t), e->delta, kHidden * sizeof(uint16_t),
                          kHidden * sizeof(uint16_t), rows, cudaMemcpyDeviceToDevice, st));
     CK(launch_linear(e->pair, e->mtp_fc, e->resid, rows, kHidden, 2048, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+    if (u_out) CK(copy_rows(u_out, e->resid, (size_t)rows * kHidden, st));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, nullptr, L.input_norm, nullptr, e->normed, rows, st));
     CK(launch_linear(e->normed, L.in_w, e->proj, rows, L.in_n, kHidden, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     AttnParams ap{};
@@ -906,10 +909,28 @@ static int draft_once(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, c
     CK(launch_linear(e->normed, L.gu_w, e->act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_linear(e->act, L.down_w, e->delta, rows, kHidden, kFF, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
     CK(launch_add_norm(e->resid, nullptr, nullptr, 0, e->delta, e->mtp_norm_out, e->resid, e->normed, rows, st));
-    int rc = run_head(e, e->normed, rows, proposal, nullptr, st);
+    int rc = run_head(e, e->normed, rows, proposal, logits_out, st);
     if (rc != Q35_OK) return rc;
-    CK(launch_add_int(m->n, 1, rows, st));
+    LAUNCH_PLAIN(launch_add_int(m->n, 1, rows, st));
+    e->n_launch += 11;                            // the block's kernels above (two norms, five projections, attention, two add + norms, fc)
     m->host_n_hi += 1;
+    m->drafts_pending += 1;
+    return Q35_OK;
+}
+
+// The same draft with the block's intermediate rows copied out, for stage-level parity against the
+// reference's taps (speccheck/mtp.py:57-83: `mtp.u`, `mtp.x_d`, `mtp.logits_last`).
+extern "C" int q35_mtp_draft_taps(q35_engine* e, q35_mtp_state* m, const uint16_t* h_norm, const int* y_next,
+                                  const int* pos, int* proposal, uint16_t* u_out, uint16_t* xd_out,
+                                  float* logits_out, void* stream) {
+    REQUIRE(e && m && h_norm && y_next && pos && proposal, Q35_ERR_ARG, "q35_mtp_draft_taps: null argument");
+    REQUIRE(m->e == e, Q35_ERR_STATE, "q35_mtp_draft_taps: state belongs to another engine");
+    REQUIRE(m->host_n_hi + 1 <= m->max_ctx, Q35_ERR_CAPACITY, "draft cache full (%d rows)", m->max_ctx);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    pdl_set_rows(m->lanes);
+    int rc = draft_once(e, m, h_norm, y_next, pos, proposal, st, u_out, logits_out);
+    if (rc != Q35_OK) return rc;
+    if (xd_out) CK(copy_rows(xd_out, e->normed, (size_t)m->lanes * kHidden, st));
     return Q35_OK;
 }
 
@@ -983,6 +1004,9 @@ extern "C" int q35_mtp_draft_k(q35_engine* e, q35_mtp_state* m, const uint16_t* 
 static int verify_round(q35_engine* e, q35_state* s, q35_mtp_state* m, const int* cur, const int* cand, int k,
                         int* emit, int* n_emit, uint16_t* h_next, cudaStream_t st) {
     const int L = s->lanes;
+    // a rejecting round drops k rows from the draft cache: they must have been drafted since the last round
+    REQUIRE(m->drafts_pending >= k, Q35_ERR_STATE, "verify of depth %d after %d draft(s): draft first (q35_mtp_draft / q35_mtp_draft_k)", k, m->drafts_pending);
+    m->drafts_pending = 0;
     verify_ids_kernel<<<(L * (k + 1) + 255) / 256, 256, 0, st>>>(cur, cand, k, e->tok2, L);
     CK(cudaGetLastError());
     int rc = run_body(e, s, e->tok2, k + 1, k, st);
@@ -992,6 +1016,7 @@ static int verify_round(q35_engine* e, q35_state* s, q35_mtp_state* m, const int
     mtp_verdict_kernel<<<(L + 7) / 8, 256, 0, st>>>(cand, e->tgt, e->normed, k, emit, n_emit, h_next,
                                                     s->pos, s->sel, m->n, L);
     CK(cudaGetLastError());
+    e->n_launch += 2;                             // the id-gather ahead of the body and the verdict
     s->host_pos_hi += k + 1;   // upper bound: lanes that rejected sit lower
     return Q35_OK;
 }
@@ -1014,6 +1039,63 @@ extern "C" int q35_mtp_verify_k(q35_engine* e, q35_state* s, q35_mtp_state* m, c
 // ------------------------------------------------------------------------------------------------
 // single stages
 // ------------------------------------------------------------------------------------------------
+extern "C" int q35_engine_launch_count(q35_engine* e, long long* count_host) {
+    REQUIRE(e && count_host, Q35_ERR_ARG, "q35_engine_launch_count: null argument");
+    *count_host = e->n_launch;
+    return Q35_OK;
+}
+
+extern "C" int q35_engine_clear_status(q35_engine* e, void* stream) {
+    REQUIRE(e, Q35_ERR_ARG, "q35_engine_clear_status: null engine");
+    CK(cudaMemsetAsync(e->dev_status, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    return Q35_OK;
+}
+
+extern "C" int q35_op_linear_resid(q35_engine* e, const uint16_t* x, const uint16_t* W, uint16_t* resid, int rows,
+                                   int K, void* stream) {
+    REQUIRE(e && x && W && resid, Q35_ERR_ARG, "q35_op_linear_resid: null argument");
+    REQUIRE(rows >= 1 && rows <= kFusedMaxRows, Q35_ERR_CAPACITY, "q35_op_linear_resid: rows = %d, supported 1..%d", rows, kFusedMaxRows);
+    REQUIRE(K == 2048 || K == 3584, Q35_ERR_ARG, "q35_op_linear_resid: K = %d unsupported", K);
+    REQUIRE(aligned16(x) && aligned16(W) && aligned16(resid), Q35_ERR_ARG, "q35_op_linear_resid: pointers must be 16-byte aligned");
+    pdl_set_rows(rows);
+    CK(launch_linear_resid_rows(x, W, resid, rows, K, nullptr, 0, static_cast<cudaStream_t>(stream)));
+    return Q35_OK;
+}
+
+extern "C" int q35_op_linear_norm(q35_engine* e, const uint16_t* resid, const uint16_t* nw, const uint16_t* W,
+                                  uint16_t* out, int rows, int N, int swiglu, void* stream) {
+    REQUIRE(e && resid && nw && W && out, Q35_ERR_ARG, "q35_op_linear_norm: null argument");
+    REQUIRE(rows >= 1 && rows <= kFusedMaxRows, Q35_ERR_CAPACITY, "q35_op_linear_norm: rows = %d, supported 1..%d", rows, kFusedMaxRows);
+    REQUIRE(N >= 8 && N % 8 == 0, Q35_ERR_ARG, "q35_op_linear_norm: N = %d must be a multiple of 8", N);
+    REQUIRE(aligned16(resid) && aligned16(W) && aligned16(out) && aligned16(nw), Q35_ERR_ARG, "q35_op_linear_norm: pointers must be 16-byte aligned");
+    pdl_set_rows(rows);
+    CK(launch_linear_norm_rows(resid, nw, W, out, rows, N, swiglu ? EPI_SWIGLU : EPI_PLAIN, nullptr, 0,
+                               static_cast<cudaStream_t>(stream)));
+    return Q35_OK;
+}
+
+// One block of the decoder in isolation, for layer-level teacher forcing: x_in [lanes*T][1024] are the
+// block's input residual rows, x_out receives its output rows; the lanes' state is read at their current
+// positions and updated (state of that layer, one KV row), the positions are NOT advanced.
+extern "C" int q35_op_layer(q35_engine* e, q35_state* s, int layer, const uint16_t* x_in, uint16_t* x_out, int T,
+                            int fused, void* stream) {
+    REQUIRE(e && s && x_in && x_out, Q35_ERR_ARG, "q35_op_layer: null argument");
+    REQUIRE(s->e == e, Q35_ERR_STATE, "q35_op_layer: state belongs to another engine");
+    REQUIRE(layer >= 0 && layer < kLayers && T >= 1, Q35_ERR_ARG, "q35_op_layer: layer %d, T %d", layer, T);
+    const int rows = s->lanes * T;
+    REQUIRE(rows <= e->max_rows, Q35_ERR_CAPACITY, "body of %d rows exceeds engine max_rows %d", rows, e->max_rows);
+    REQUIRE(s->host_pos_hi + T <= s->max_ctx, Q35_ERR_CAPACITY, "position %d + %d beyond max_ctx %d", s->host_pos_hi, T, s->max_ctx);
+    const bool use_fused = fused < 0 ? body_fused(e, rows) : (fused != 0 && rows <= kFusedMaxRows);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    pdl_set_rows(rows);
+    CK(launch_add_norm(x_in, nullptr, nullptr, 0, nullptr, e->layers[layer].input_norm, e->resid, e->normed, rows, st));
+    const uint16_t* next_norm = (layer + 1 < kLayers) ? e->layers[layer + 1].input_norm : e->final_norm;
+    int rc = run_layer(e, s, layer, T, 0, use_fused, true, next_norm, nullptr, 0, st);
+    if (rc != Q35_OK) return rc;
+    CK(copy_rows(x_out, e->resid, (size_t)rows * kHidden, st));
+    return Q35_OK;
+}
+
 extern "C" int q35_op_add_norm(const uint16_t* x, const uint16_t* delta, const uint16_t* w,
                                uint16_t* sum_out, uint16_t* normed_out, int rows, void* stream) {
     REQUIRE(x && w && rows >= 1, Q35_ERR_ARG, "q35_op_add_norm: bad argument");

@@ -375,19 +375,18 @@ cudaError_t launch_gdn_step(const GdnParams& p, cudaStream_t st) {
         for (int b = 0; b <= p.checkpoint; ++b)
             if (p.S[b] == nullptr || p.win[b] == nullptr) return cudaErrorInvalidValue;
     }
-    static int max_ctas = 0;
-    if (max_ctas == 0) {
-        int dev = 0, sms = 0;
-        cudaError_t e = cudaGetDevice(&dev);
-        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gdn_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGdnSmemBytes);
+    static bool attr_done[kMaxDevices] = {false};           // per device
+    {
+        cudaError_t e = opt_in_smem(gdn_step_kernel, kGdnSmemBytes, attr_done);
         if (e != cudaSuccess) return e;
-        int per_sm = 2;
-        if (const char* env = std::getenv("Q35_GDN_CTAS_PER_SM")) per_sm = env[0] == '1' ? 1 : 2;   // tuning knob
-        max_ctas = (per_sm * sms / kGdnHeads) * kGdnHeads;  // two CTAs per SM, rounded down to whole lanes
-        if (max_ctas < kGdnHeads) max_ctas = kGdnHeads;
     }
+    static int per_sm = 0;                                  // tuning knob, read once: Q35_GDN_CTAS_PER_SM = 1 or 2
+    if (per_sm == 0) {
+        const char* env = std::getenv("Q35_GDN_CTAS_PER_SM");
+        per_sm = (env != nullptr && env[0] == '1') ? 1 : 2;
+    }
+    int max_ctas = (per_sm * sm_count() / kGdnHeads) * kGdnHeads;   // two CTAs per SM, rounded down to whole lanes
+    if (max_ctas < kGdnHeads) max_ctas = kGdnHeads;
     const int items = p.lanes * kGdnHeads;
     const int grid = items < max_ctas ? items : max_ctas;
     CUtensorMap pmap, wmap[kStateBufs];

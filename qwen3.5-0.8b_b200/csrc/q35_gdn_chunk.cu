@@ -998,13 +998,11 @@ cudaError_t gdn_chunk_init(cudaStream_t st) {
 
 cudaError_t launch_gdn_chunked(const GdnParams& p, cudaStream_t st) {
     if (p.lanes <= 0 || p.T <= 0 || p.lanes > 65535 || p.checkpoint) return cudaErrorInvalidValue;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(gdn_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kChunkSmem);
+    {
+        static bool simt_done[kMaxDevices] = {false}, tc_done[kMaxDevices] = {false};     // per device
+        cudaError_t e = opt_in_smem(gdn_chunk_kernel, kChunkSmem, simt_done);
+        if (e == cudaSuccess) e = opt_in_smem(gdn_chunk_tc_kernel, kChunkTcSmem, tc_done);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(gdn_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kChunkTcSmem);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
     }
     {
         cudaError_t e = gdn_chunk_init(st);         // no-op once this device's table is filled

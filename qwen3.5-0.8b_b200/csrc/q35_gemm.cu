@@ -38,20 +38,72 @@ __device__ __forceinline__ uint4 ldg16(const uint16_t* p) {
     return __ldg(reinterpret_cast<const uint4*>(p));
 }
 
+// eight residual values -> bf16( (v * inv) * (1 + w) ), the zero-centred RMSNorm's element rule
+__device__ __forceinline__ uint32_t norm2(uint32_t v, float inv, uint32_t w) {
+    return pack_bf2(__fmul_rn(__fmul_rn(lo_bf(v), inv), 1.0f + lo_bf(w)),
+                    __fmul_rn(__fmul_rn(hi_bf(v), inv), 1.0f + hi_bf(w)));
+}
+__device__ __forceinline__ float sumsq8(const uint4& v) {
+    float a = lo_bf(v.x) * lo_bf(v.x);
+    a += hi_bf(v.x) * hi_bf(v.x);
+    a += lo_bf(v.y) * lo_bf(v.y); a += hi_bf(v.y) * hi_bf(v.y);
+    a += lo_bf(v.z) * lo_bf(v.z); a += hi_bf(v.z) * hi_bf(v.z);
+    a += lo_bf(v.w) * lo_bf(v.w); a += hi_bf(v.w) * hi_bf(v.w);
+    return a;
+}
+__device__ __forceinline__ uint4 norm8(const uint4& v, float inv, const uint4& w) {
+    return make_uint4(norm2(v.x, inv, w.x), norm2(v.y, inv, w.y), norm2(v.z, inv, w.z), norm2(v.w, inv, w.w));
+}
+
 // ------------------------------------------------------------------------------------------------
 // rows <= 16: weight-streaming form
 // ------------------------------------------------------------------------------------------------
-template <int K, int NB, int EPI>
-__global__ void __launch_bounds__(256)
+// NORM: the x rows are un-normalised residual rows; the kernel applies the zero-centred RMSNorm
+// (weights nw) while it stages them.  Every CTA holds all of x, so it takes the rows' sums of squares
+// from its own registers (per thread, then across the four lanes that share a row, then across the
+// eight warps in warp order: deterministic) - no extra pass over memory.
+// EPI_RESID: `out` is the residual stream [M][N], updated in place: resid = bf16(resid + bf16(dot)).
+// pf / pf_bytes: weights of a LATER kernel of the body; the CTAs ask the L2 for them (one slice each)
+// as soon as their own loads are issued, so that the later kernel streams from L2 while HBM runs ahead
+// of the chain of dependent kernels.
+struct GemvExtra {
+    const uint16_t* nw;        // NORM: norm weights [K]
+    const void* pf;            // optional: bytes to pull into L2
+    unsigned long long pf_bytes;
+    int trigger_early;         // 1: let the successor start right after this kernel's own wait
+};
+
+__device__ __forceinline__ void l2_prefetch_slice(const void* base, unsigned long long total, int part, int n_parts) {
+    // slice `part` of n_parts, in pieces of at most 32 KiB (sizes multiples of 16 bytes)
+    const unsigned long long per = ((total / n_parts) + 15ull) & ~15ull;
+    unsigned long long off = per * part;
+    if (off >= total) return;
+    unsigned long long left = total - off < per ? total - off : per;
+    left &= ~15ull;
+    const char* p = static_cast<const char*>(base) + off;
+    while (left > 0) {
+        const unsigned n = left > 32768ull ? 32768u : (unsigned)left;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(n) : "memory");
+        p += n;
+        left -= n;
+    }
+}
+
+template <int K, int NB, int EPI, bool NORM>
+__global__ void __launch_bounds__(256, 2)
 gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W, void* __restrict__ out,
-                 int M, int N, ArgMax* __restrict__ partials, float* __restrict__ logits, int n_parts) {
+                 int M, int N, ArgMax* __restrict__ partials, float* __restrict__ logits, int n_parts,
+                 GemvExtra ex) {
     constexpr int KW = K / 8;       // k range of one warp
     constexpr int CH = KW / 32;     // 32-wide k chunks per warp
     constexpr int BATCH = (CH <= 8) ? CH : 7;
     static_assert(CH % BATCH == 0, "chunk batching");
+    static_assert(!NORM || CH == BATCH, "the normalising form stages all of x in one batch");
     constexpr int COLS = 8 * NB;
 
     __shared__ float red[8][16][COLS];
+    __shared__ float ss_part[NORM ? 8 : 1][16];
+    __shared__ __align__(16) uint16_t nw_s[NORM ? K : 8];       // norm weights, staged once per CTA (not held in registers across the wait)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -76,6 +128,8 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
         for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
 
     const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    uint16_t r_old = 0;                  // EPI_RESID: this thread's element of the residual stream
+    const int e_row = threadIdx.x / COLS, e_col = threadIdx.x % COLS;
 #pragma unroll 1
     for (int c0 = 0; c0 < CH; c0 += BATCH) {
         uint4 wv[NB][BATCH];
@@ -83,12 +137,43 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
         for (int c = 0; c < BATCH; ++c)
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) wv[nb][c] = ldg16(wrow[nb] + (c0 + c) * 32);
-        if (c0 == 0) pdl_wait();          // the first batch of weight loads flies while the producer of x drains
+        if (NORM && threadIdx.x < K / 8)          // immutable: ahead of the wait
+            *reinterpret_cast<uint4*>(&nw_s[threadIdx.x * 8]) = ldg16(ex.nw + threadIdx.x * 8);
+        if (c0 == 0) {
+            if (ex.pf != nullptr && threadIdx.x == 0) l2_prefetch_slice(ex.pf, ex.pf_bytes, blockIdx.x, gridDim.x);
+            pdl_wait();                   // the first batch of weight loads flies while the producer of x drains
+            if (ex.trigger_early) pdl_trigger();
+        }
         uint4 xl[BATCH], xh[BATCH];
 #pragma unroll
         for (int c = 0; c < BATCH; ++c) {
             xl[c] = lo_ok ? __ldcg(reinterpret_cast<const uint4*>(xlo + (c0 + c) * 32)) : zero4;
             xh[c] = hi_ok ? __ldcg(reinterpret_cast<const uint4*>(xhi + (c0 + c) * 32)) : zero4;
+        }
+        if (EPI == EPI_RESID && c0 == 0 && threadIdx.x < 16 * COLS && e_row < M && n0 + e_col < N)
+            r_old = __ldcg(static_cast<const uint16_t*>(out) + (size_t)e_row * N + n0 + e_col);
+        if (NORM) {
+            // rows g and g + 8: this thread's 32 values each, then lanes t = 0..3, then the eight warps
+            float sl = 0.f, sh = 0.f;
+#pragma unroll
+            for (int c = 0; c < BATCH; ++c) {
+                sl += sumsq8(xl[c]);
+                sh += sumsq8(xh[c]);
+            }
+            sl += __shfl_xor_sync(0xffffffffu, sl, 1); sl += __shfl_xor_sync(0xffffffffu, sl, 2);
+            sh += __shfl_xor_sync(0xffffffffu, sh, 1); sh += __shfl_xor_sync(0xffffffffu, sh, 2);
+            if (t == 0) { ss_part[warp][g] = sl; ss_part[warp][g + 8] = sh; }
+            __syncthreads();
+            float al = 0.f, ah = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) { al += ss_part[w][g]; ah += ss_part[w][g + 8]; }
+            const float il = rsqrt_acc(al * (1.0f / K) + kEps), ih = rsqrt_acc(ah * (1.0f / K) + kEps);
+#pragma unroll
+            for (int c = 0; c < BATCH; ++c) {
+                const uint4 nwv = *reinterpret_cast<const uint4*>(&nw_s[kbase + c * 32]);     // staged before the barrier above
+                xl[c] = norm8(xl[c], il, nwv);
+                xh[c] = norm8(xh[c], ih, nwv);
+            }
         }
 #pragma unroll
         for (int c = 0; c < BATCH; ++c)
@@ -100,7 +185,7 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
                 mma16816(acc[nb], xl[c].z, xh[c].z, xl[c].w, xh[c].w, wv[nb][c].z, wv[nb][c].w);
             }
     }
-    pdl_trigger();          // all loads are done: the successor may start fetching its weights
+    if (!ex.trigger_early) pdl_trigger();          // all loads are done: the successor may start fetching its weights
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
         red[warp][g][nb * 8 + 2 * t] = acc[nb][0];
@@ -110,7 +195,16 @@ gemv_rows_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ W,
     }
     __syncthreads();
 
-    if (EPI == EPI_SWIGLU) {
+    if (EPI == EPI_RESID) {
+        // thread = (row, column) of the CTA's 16 x COLS outputs; whole warps take part in the shuffles
+        if (threadIdx.x < 16 * COLS) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s += red[w][e_row][e_col];
+            if (e_row < M && n0 + e_col < N)
+                static_cast<uint16_t*>(out)[(size_t)e_row * N + n0 + e_col] = f2bf(bf2f(r_old) + bfround(s));
+        }
+    } else if (EPI == EPI_SWIGLU) {
         uint16_t* o = static_cast<uint16_t*>(out);
         const int ldo = N >> 1;
         for (int idx = threadIdx.x; idx < 16 * (COLS / 2); idx += 256) {
@@ -384,38 +478,49 @@ __global__ void pack_gate_up_kernel(const uint4* __restrict__ gate, const uint4*
 // ------------------------------------------------------------------------------------------------
 // host-side selection
 // ------------------------------------------------------------------------------------------------
-template <int K, int NB, int EPI>
+// A weight-streaming kernel lets its successor start right after its own wait: the successor's weight
+// loads then overlap this kernel's arithmetic and tail (0.79 -> 0.75 ms per 1-lane step, 0.97 -> 0.92 ms
+// at 16 lanes), and still only one successor is resident.  Q35_TRIG=0: after its arithmetic.
+static int trigger_early() {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* env = std::getenv("Q35_TRIG");
+        mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    return mode;
+}
+
+template <int K, int NB, int EPI, bool NORM = false>
 static cudaError_t run_gemv(const uint16_t* x, const uint16_t* W, void* out, int M, int N,
-                            ArgMax* partials, float* logits, int n_parts, cudaStream_t st) {
+                            ArgMax* partials, float* logits, int n_parts, cudaStream_t st,
+                            const uint16_t* nw = nullptr, const void* pf = nullptr, size_t pf_bytes = 0) {
     const int grid = (N + 8 * NB - 1) / (8 * NB);
-    return launch_k(gemv_rows_kernel<K, NB, EPI>, dim3(grid), dim3(256), 0, st, x, W, out, M, N, partials, logits, n_parts);
+    const GemvExtra ex{nw, pf, (unsigned long long)pf_bytes, trigger_early()};
+    return launch_k(gemv_rows_kernel<K, NB, EPI, NORM>, dim3(grid), dim3(256), 0, st, x, W, out, M, N, partials,
+                    logits, n_parts, ex);
 }
 
 template <int BM, int BN, int WARPS_M, int NWARPS, int STAGES, int EPI>
 static cudaError_t run_tiled(const uint16_t* x, const uint16_t* W, void* out, int M, int N, int K,
                              ArgMax* partials, float* logits, int n_parts, cudaStream_t st) {
     constexpr size_t smem = (size_t)STAGES * (BM + BN) * 64 * sizeof(uint16_t);
-    static bool attr_done = false;   // per instantiation; set once per process
+    static bool attr_done[kMaxDevices] = {false};   // per instantiation and device
     auto kern = gemm_tiled_kernel<BM, BN, WARPS_M, NWARPS, STAGES, EPI>;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attr_done = true;
-    }
+    cudaError_t e = opt_in_smem(kern, smem, attr_done);
+    if (e != cudaSuccess) return e;
     dim3 grid((M + BM - 1) / BM, (N + BN - 1) / BN);
     return launch_k(kern, grid, dim3(NWARPS * 32), smem, st, x, W, out, M, N, K, partials, logits, n_parts);
 }
-
-static inline int gemv_nb(int K) { return K == 1024 ? 4 : 1; }
 
 // tile choice of the tiled form: the largest tile whose grid still covers the SMs
 struct TileChoice { int bm, bn; };
 static TileChoice choose_tile(int M, int N) {
     auto ctas = [&](int bm, int bn) { return ((M + bm - 1) / bm) * ((N + bn - 1) / bn); };
-    if (M > 64 && ctas(128, 128) >= 148) return {128, 128};
-    if (M > 32 && ctas(64, 128) >= 148) return {64, 128};
-    if (ctas(32, 128) >= 148 || N > 2048) return {32, 128};
-    if (M > 32 && ctas(64, 32) >= 148) return {64, 32};
+    const int sms = sm_count();
+    if (M > 64 && ctas(128, 128) >= sms) return {128, 128};
+    if (M > 32 && ctas(64, 128) >= sms) return {64, 128};
+    if (ctas(32, 128) >= sms || N > 2048) return {32, 128};
+    if (M > 32 && ctas(64, 32) >= sms) return {64, 32};
     return {32, 32};
 }
 
@@ -480,6 +585,28 @@ cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int r
         case EPI_SWIGLU: return dispatch<EPI_SWIGLU>(x, W, out, rows, N, K, partials, logits, n_parts, st);
         case EPI_ARGMAX: return dispatch<EPI_ARGMAX>(x, W, out, rows, N, K, partials, logits, n_parts, st);
     }
+    return cudaErrorInvalidValue;
+}
+
+// ---- fused residual stream (few rows) ---------------------------------------------------------
+// Producer: resid [rows][1024] += x [rows][K] . W[1024][K]^T in place.  Consumer: out = N(resid; nw) . W^T
+// with the norm applied while the rows are staged (every CTA holds all rows, so it takes their sums of
+// squares from its own registers).  Between them no add + norm kernel runs.  pf / pf_bytes: weights of a
+// later kernel to pull into L2 (optional).
+cudaError_t launch_linear_resid_rows(const uint16_t* x, const uint16_t* W, uint16_t* resid, int rows, int K,
+                                     const void* pf, size_t pf_bytes, cudaStream_t st) {
+    if (rows < 1 || rows > 16) return cudaErrorInvalidValue;
+    if (K == 2048) return run_gemv<2048, 1, EPI_RESID>(x, W, resid, rows, kHidden, nullptr, nullptr, 0, st, nullptr, pf, pf_bytes);
+    if (K == 3584) return run_gemv<3584, 1, EPI_RESID>(x, W, resid, rows, kHidden, nullptr, nullptr, 0, st, nullptr, pf, pf_bytes);
+    return cudaErrorInvalidValue;
+}
+cudaError_t launch_linear_norm_rows(const uint16_t* resid, const uint16_t* nw, const uint16_t* W, void* out, int rows,
+                                    int N, int epi, const void* pf, size_t pf_bytes, cudaStream_t st) {
+    if (rows < 1 || rows > 16 || N <= 0 || (N & 7)) return cudaErrorInvalidValue;
+    if (epi == EPI_PLAIN)
+        return run_gemv<1024, 4, EPI_PLAIN, true>(resid, W, out, rows, N, nullptr, nullptr, 0, st, nw, pf, pf_bytes);
+    if (epi == EPI_SWIGLU)
+        return run_gemv<1024, 4, EPI_SWIGLU, true>(resid, W, out, rows, N, nullptr, nullptr, 0, st, nw, pf, pf_bytes);
     return cudaErrorInvalidValue;
 }
 

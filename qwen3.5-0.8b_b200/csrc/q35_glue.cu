@@ -12,9 +12,21 @@ namespace q35 {
 // most kPdlAutoRows rows turns it on for its own launches.
 namespace {
 constexpr int kPdlAutoRows = 192;
-int g_pdl_rows = 1 << 30;
+thread_local int g_pdl_rows = 1 << 30;      // per host thread: two engines driven by two threads do not share it
 }
 void pdl_set_rows(int rows) { g_pdl_rows = rows; }
+
+int sm_count() {
+    static int sms[kMaxDevices] = {0};
+    const int dev = current_device_slot();
+    if (dev < 0) return 148;
+    if (sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
 bool pdl_enabled() {
     static int v = -2;
     if (v == -2) {

@@ -59,7 +59,7 @@ class Census(C.Structure):
 
 EXPORTS = [
     "q35_last_error", "q35_abi_version", "q35_engine_create", "q35_engine_destroy", "q35_step_census",
-    "q35_profile_begin", "q35_profile_end", "q35_engine_status", "q35_small_step_trace",
+    "q35_profile_begin", "q35_profile_end", "q35_engine_status",
     "q35_state_sizes_of", "q35_state_create", "q35_state_destroy", "q35_state_reset",
     "q35_state_positions", "q35_state_note_advance", "q35_state_export_lane", "q35_state_import_lane",
     "q35_decode_step", "q35_prefill", "q35_mtp_state_create", "q35_mtp_state_destroy",
@@ -68,7 +68,8 @@ EXPORTS = [
     "q35_mtp_state_note_advance",
     "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
-    "q35_lm_head_argmax_static",
+    "q35_lm_head_argmax_static", "q35_engine_clear_status", "q35_engine_launch_count",
+    "q35_mtp_draft_taps", "q35_op_linear_resid", "q35_op_linear_norm", "q35_op_layer",
 ]
 
 _lib = None
@@ -300,16 +301,19 @@ class Engine:
             raise Q35Error(1, "checkpoint verification failed: " + "; ".join(stats.verify_failures[:3]))
         return cls(store.checkpoint_dict(), max_rows=max_rows, mtp=mtp), stats
 
-    def small_step_trace(self, n: int = 320):
-        """Nanosecond clock of CTA 0 at every barrier of the last profiled few-lane step."""
-        buf = (C.c_ulonglong * n)()
-        _check(self.lib.q35_small_step_trace(self.handle, buf, n))
-        return list(buf)
-
     def status(self) -> int:
         """0 when healthy; non-zero when a kernel's bounded wait expired (synchronises the device)."""
         v = C.c_int(0)
         _check(self.lib.q35_engine_status(self.handle, C.byref(v)))
+        return v.value
+
+    def clear_status(self):
+        _check(self.lib.q35_engine_clear_status(self.handle, _stream()))
+
+    def launch_count(self) -> int:
+        """Kernels enqueued through this engine so far (a captured kernel counts once, at capture)."""
+        v = C.c_longlong(0)
+        _check(self.lib.q35_engine_launch_count(self.handle, C.byref(v)))
         return v.value
 
     # ---- census -------------------------------------------------------------------------------
@@ -324,7 +328,7 @@ class Engine:
         c = self.census()
         return c["weight_bytes"] + lanes * (c["lane_state_bytes"] + c["kv_bytes_per_pos"] * (ctx + 1))
 
-    FAMILIES = ["glue", "in_proj", "gdn", "attn", "out_proj", "mlp_gateup", "mlp_down", "head", "step_kernel"]
+    FAMILIES = ["glue", "in_proj", "gdn", "attn", "out_proj", "mlp_gateup", "mlp_down", "head"]
 
     def profile_begin(self):
         _check(self.lib.q35_profile_begin(self.handle))
@@ -431,6 +435,36 @@ class Engine:
         _check(self.lib.q35_pack_gate_up(_ptr(gate), _ptr(up), _ptr(out), _stream()))
         return out
 
+    def op_linear_resid(self, x, Wt, resid):
+        """resid [rows, 1024] += x @ Wt.T in place (bf16 roundings of the reference); returns resid."""
+        _check(self.lib.q35_op_linear_resid(self.handle, _ptr(x), _ptr(Wt), _ptr(resid), x.shape[0], Wt.shape[1], _stream()))
+        return resid
+
+    def op_linear_norm(self, resid, nw, Wt, swiglu: bool = False):
+        """N(resid; nw) @ Wt.T for the rows the last op_linear_resid produced."""
+        n_out = Wt.shape[0] // 2 if swiglu else Wt.shape[0]
+        out = torch.empty((resid.shape[0], n_out), dtype=torch.bfloat16, device="cuda")
+        _check(self.lib.q35_op_linear_norm(self.handle, _ptr(resid), _ptr(nw), _ptr(Wt), _ptr(out), resid.shape[0],
+                                           Wt.shape[0], int(swiglu), _stream()))
+        return out
+
+    def op_layer(self, state: "LaneState", layer: int, x_in, T: int = 1, fused: int = -1):
+        """One decoder block on its input residual rows x_in [lanes*T, 1024]; positions are not advanced."""
+        out = torch.empty_like(x_in)
+        _check(self.lib.q35_op_layer(self.handle, state.handle, layer, _ptr(x_in), _ptr(out), T, fused, _stream()))
+        return out
+
+    def mtp_draft_taps(self, m: "MtpState", h_norm, y_next, pos, want_logits: bool = False):
+        """One draft with the block's taps: (proposal, u, x_d, logits or None)."""
+        L = m.state.lanes
+        prop = torch.empty(L, dtype=torch.int32, device="cuda")
+        u = torch.empty((L, 1024), dtype=torch.bfloat16, device="cuda")
+        xd = torch.empty((L, 1024), dtype=torch.bfloat16, device="cuda")
+        lg = torch.empty((L, self.vocab), dtype=torch.float32, device="cuda") if want_logits else None
+        _check(self.lib.q35_mtp_draft_taps(self.handle, m.handle, _ptr(h_norm), _ptr(y_next), _ptr(pos), _ptr(prop),
+                                           _ptr(u), _ptr(xd), _ptr(lg), _stream()))
+        return prop, u, xd, lg
+
     def op_mlp_gateup(self, x, Wgu):
         act = torch.empty((x.shape[0], W.D_FF), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.q35_op_mlp_gateup(_ptr(x), _ptr(Wgu), _ptr(act), x.shape[0], _stream()))
@@ -485,9 +519,11 @@ class StepGraph:
         self.tok_out = self.buf[steps % 2]
         self.graph = torch.cuda.CUDAGraph()
         self.replays = 0
+        before = engine.launch_count()
         with torch.cuda.graph(self.graph):
             for i in range(steps):
                 engine.decode_step(state, self.buf[i % 2], self.buf[(i + 1) % 2])
+        self.kernels_per_replay = engine.launch_count() - before     # counted while the graph was captured
         # capture ran no kernel but advanced the host-side position bound once per captured step: take
         # that back, every replay reports itself (so a bound tightened between capture and replay stays right)
         state.note_advance(-steps)

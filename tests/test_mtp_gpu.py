@@ -32,6 +32,26 @@ def bf(a):
     return torch.from_numpy(np.asarray(a)).to(torch.bfloat16)
 
 
+_W = {}
+
+
+def eng_fc_weight(eng):
+    return _W.get("mtp.fc.weight")
+
+
+def eng_norm(eng, name):
+    return _W["mtp." + name + ".weight"]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _mtp_weights(weights):
+    for k, v in weights.items():
+        if k.startswith("mtp."):
+            _W[k] = v
+    yield
+    _W.clear()
+
+
 def prompts(golden, lanes):
     base = torch.from_numpy(golden["mtp"]["prompt"]).int()
     gen = torch.Generator().manual_seed(17)
@@ -40,13 +60,50 @@ def prompts(golden, lanes):
 
 
 def test_draft_matches_reference(eng, golden):
-    """One draft call on the reference's own (h, y_next, pos): same proposal id."""
+    """One draft call on the reference's own (h, y_next, pos): same proposal id, and the block's taps
+    (speccheck/mtp.py:57-83) within the stage tolerance: u = fc([N(E[y]) | N(h)]) - a swapped operand
+    order shows here at once -, the final-norm row x_d, and the sub-sampled logits."""
     g = golden["mtp"]
     st = eng.allocate_state(1, 64)
     m = eng.mtp_allocate(st, 64)
-    prop = eng.mtp_draft(m, bf(g["draft_h"]).cuda(), torch.tensor(g["draft_y"], dtype=torch.int32).cuda(),
-                         torch.tensor(g["draft_pos"], dtype=torch.int32).cuda())
+    h, y = bf(g["draft_h"]).cuda(), torch.tensor(g["draft_y"], dtype=torch.int32).cuda()
+    pos = torch.tensor(g["draft_pos"], dtype=torch.int32).cuda()
+    prop, u, xd, lg = eng.mtp_draft_taps(m, h, y, pos, want_logits=True)
     assert int(prop[0]) == int(g["draft_id"][0])
+    e_u = rel_l2(u.float().cpu(), g["draft_u"])
+    e_x = rel_l2(xd.float().cpu(), g["draft_xd"])
+    e_l = rel_l2(lg.cpu()[:, ::97], g["draft_logits_sub"])
+    assert e_u <= 1e-2 and e_x <= 1e-2 and e_l <= 1e-2, (e_u, e_x, e_l)
+    # the wrong operand order [N(h) | N(E[y])] is far outside that band: the check bites
+    swapped_u = None
+    fc = eng_fc_weight(eng)
+    if fc is not None:
+        ne = O.norm_zc(eng.embed[int(y[0])].cpu()[None], eng_norm(eng, "pre_fc_norm_embedding"))
+        nh = O.norm_zc(h.cpu(), eng_norm(eng, "pre_fc_norm_hidden"))
+        swapped_u = (torch.cat([nh, ne], -1) @ fc.t()).float()
+        assert rel_l2(swapped_u, g["draft_u"]) > 0.5
+    m.close()
+    st.close()
+
+
+def test_verify_without_draft_is_refused(eng, pkg, golden):
+    """A rejecting round drops k rows from the draft cache, so a verify that no draft preceded is
+    refused on the host (status 4) instead of driving the cache length negative."""
+    ids = prompts(golden, 2)
+    st = eng.allocate_state(2, 64)
+    m = eng.mtp_allocate(st, 64)
+    t, h = eng.prefill(st, ids, want_normed=True)
+    with pytest.raises(pkg.Q35Error) as ei:
+        eng.mtp_verify(st, m, t, t)
+    assert ei.value.code == 4
+    d = eng.mtp_draft(m, h, t, (st.positions + 1).int())
+    eng.mtp_verify(st, m, t, d)                       # one draft: one verify is fine
+    with pytest.raises(pkg.Q35Error):
+        eng.mtp_verify(st, m, t, d)                   # ... a second one is not
+    m.reset()
+    with pytest.raises(pkg.Q35Error):
+        eng.mtp_verify(st, m, t, d)
+    assert eng.status() == 0
     m.close()
     st.close()
 

@@ -26,10 +26,12 @@ REPORT = {}
 
 
 def note(key, val):
+    """Measured parity figures; written to $Q35_REPORT_DIR/parity_ops.json when that variable is set."""
     REPORT[key] = val
-    out = REPO / "gpurun_out"
-    out.mkdir(exist_ok=True)
-    (out / "parity_ops.json").write_text(json.dumps(REPORT, indent=1, sort_keys=True))
+    out = os.environ.get("Q35_REPORT_DIR")
+    if out:
+        Path(out).mkdir(parents=True, exist_ok=True)
+        (Path(out) / "parity_ops.json").write_text(json.dumps(REPORT, indent=1, sort_keys=True))
 
 
 def bf(a):
@@ -100,6 +102,68 @@ def test_linear_shapes(eng, rows):
         # against torch's own bf16 matmul (what the oracle executes)
         assert rel_l2(out, (x @ Wt.t()).float()) < 1e-2
     note(f"linear_rows{rows}_worst_rel_l2", worst)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 7, 8, 9, 15, 16])
+def test_fused_residual_stream(eng, rows):
+    """The fused residual stream of few-row bodies as two stages: the output / down projection adds into
+    the residual rows in place, and the next projection normalises those rows while it stages them.  The normalised rows are read back exactly
+    through an identity weight matrix; the projections are checked against f64 matmuls."""
+    for K in (2048, 3584):
+        g = torch.Generator().manual_seed(K + rows)
+        x = torch.randn((rows, K), generator=g).to(torch.bfloat16)
+        Wt = (torch.randn((1024, K), generator=g) * 0.02).to(torch.bfloat16)
+        r0 = torch.randn((rows, 1024), generator=g).to(torch.bfloat16)
+        nw = (torch.randn(1024, generator=g) * 0.1).to(torch.bfloat16)
+        resid = cu(r0.clone())
+        eng.op_linear_resid(cu(x), cu(Wt), resid)
+        delta = (x.double() @ Wt.double().t()).float().to(torch.bfloat16)
+        ref = r0 + delta                                        # bf16 add, one rounding
+        got = resid.cpu()
+        # a re-associated f32 dot may round the bf16 delta the other way: rare differences of one ULP of the
+        # larger addend, nothing beyond
+        diff = (got.float() - ref.float()).abs()
+        ulp = 2.0 ** -7 * (r0.float().abs() + delta.float().abs())
+        assert bool((diff <= ulp).all()) and float((diff > 0).float().mean()) < 0.03, (rows, K, float(diff.max()))
+        assert rel_l2(got.float(), ref.float()) < 2e-3
+        # consumer, identity weights: out == N(resid; nw) bit for bit up to the order of the sum of squares
+        eye = torch.eye(1024).to(torch.bfloat16)
+        normed = eng.op_linear_norm(resid, cu(nw), cu(eye)).cpu()
+        ref_n = O.norm_zc(got, nw)
+        ulp_n = (normed.view(torch.int16).int() - ref_n.view(torch.int16).int()).abs()
+        assert int(ulp_n.max()) <= 1 and float((ulp_n > 0).float().mean()) < 0.02, (rows, K, int(ulp_n.max()))
+        # consumer, ragged in-projection width and the SwiGLU form
+        Wn = (torch.randn((8224, 1024), generator=g) * 0.02).to(torch.bfloat16)
+        out = eng.op_linear_norm(resid, cu(nw), cu(Wn)).float().cpu()
+        ref_o = (ref_n.double() @ Wn.double().t()).float().to(torch.bfloat16).float()
+        e_o = rel_l2(out, ref_o)
+        assert e_o < 5e-3, (rows, K, e_o)
+        Wg = (torch.randn((3584, 1024), generator=g) * 0.02).to(torch.bfloat16)
+        Wu = (torch.randn((3584, 1024), generator=g) * 0.02).to(torch.bfloat16)
+        Wgu = eng.pack_gate_up(cu(Wg), cu(Wu))
+        act = eng.op_linear_norm(resid, cu(nw), Wgu, swiglu=True).float().cpu()
+        ref_a = (torch.nn.functional.silu(ref_n @ Wg.t()) * (ref_n @ Wu.t())).float()
+        e_a = rel_l2(act, ref_a)
+        assert e_a < 1e-2, (rows, K, e_a)
+        note(f"fused_stream_rows{rows}_K{K}", [rel_l2(got.float(), ref.float()), e_o, e_a])
+
+
+def test_fused_residual_stream_matches_add_norm_kernels(eng):
+    """Same rows through both routes: projection + add + norm kernels vs the fused pair."""
+    for rows in (1, 3, 16):
+        g = torch.Generator().manual_seed(900 + rows)
+        x = cu(torch.randn((rows, 2048), generator=g).to(torch.bfloat16))
+        Wt = cu((torch.randn((1024, 2048), generator=g) * 0.02).to(torch.bfloat16))
+        r0 = cu(torch.randn((rows, 1024), generator=g).to(torch.bfloat16))
+        nw = cu((torch.randn(1024, generator=g) * 0.1).to(torch.bfloat16))
+        delta = eng.op_linear(x, Wt)
+        s_ref, n_ref = eng.op_add_norm(r0, delta, nw)
+        resid = r0.clone()
+        eng.op_linear_resid(x, Wt, resid)
+        eye = cu(torch.eye(1024).to(torch.bfloat16))
+        normed = eng.op_linear_norm(resid, nw, eye)
+        assert rel_l2(resid.float().cpu(), s_ref.float().cpu()) < 2e-3
+        assert rel_l2(normed.float().cpu(), n_ref.float().cpu()) < 3e-3
 
 
 @pytest.mark.parametrize("rows", [1999, 4032])
