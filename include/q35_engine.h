@@ -267,6 +267,14 @@ int q35_op_linear_resid(q35_engine* e, const uint16_t* x, const uint16_t* W, uin
                         int K, void* stream);
 int q35_op_linear_norm(q35_engine* e, const uint16_t* resid, const uint16_t* nw, const uint16_t* W,
                        uint16_t* out, int rows, int N, int swiglu, void* stream);
+/* The attention / GDN output projection or the MLP down projection as a body runs it, residual add
+ * and the following norm included (decode_step.h:9-15: "add after mixer fused with post-attn norm, add
+ * after MLP fused with the next input norm"): resid [rows][1024] updated in place; normed [rows][1024]
+ * written above 16 rows (at most 16 rows the next projection applies the norm itself and normed is
+ * left untouched).  q35_op_proj_residual_route names the kernels that stage takes. */
+int q35_op_proj_residual(q35_engine* e, const uint16_t* x, const uint16_t* W, uint16_t* resid,
+                         const uint16_t* nw, uint16_t* normed, int rows, int K, void* stream);
+const char* q35_op_proj_residual_route(q35_engine* e, int rows, int K);
 /* One decoder block in isolation (Forward._layer, speccheck/specimpl.py:426-451; the per-layer
  * teacher-forcing taps L{l}.s_in -> L{l}.s_out): x_in [lanes*T][1024] = the block's input residual
  * rows, x_out = its output rows.  Reads the lanes' state at their current positions and updates that
@@ -274,6 +282,10 @@ int q35_op_linear_norm(q35_engine* e, const uint16_t* resid, const uint16_t* nw,
  * residual stream, -1 = what a body of this size takes. */
 int q35_op_layer(q35_engine* e, q35_state* s, int layer, const uint16_t* x_in, uint16_t* x_out, int T,
                  int fused, void* stream);
+/* Name of the kernel q35_op_linear (epilogue 0), q35_op_mlp_gateup (1) or q35_op_lm_head (2) routes a
+ * shape to; a static string.  The reference routes by row count too (proj_rows vs its library GEMM,
+ * engine/kernels_gemm.cpp:852-885) and prints the route in its stage census. */
+const char* q35_op_linear_route(int rows, int N, int K, int epilogue);
 /* mlp_gateup (engine/kernels.h:363-374): act [rows][3584] from x [rows][1024]; Wgu is the
  * row-interleaved matrix q35_pack_gate_up writes ([7168][1024]: row 2f = gate f, 2f+1 = up f). */
 int q35_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16_t* Wgu, void* stream);

@@ -184,6 +184,8 @@ enum Epilogue { EPI_PLAIN = 0, EPI_SWIGLU = 1, EPI_ARGMAX = 2, EPI_PARTIAL = 3, 
 cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K,
                           int epi, ArgMax* partials, float* logits, int* n_parts, cudaStream_t st,
                           int* status = nullptr);
+const char* linear_route(int rows, int N, int K, int epi);      // name of the kernel launch_linear picks
+const char* linear_tc_route(int rows, int N, int epi);
 // tcgen05 / TMEM form (q35_gemm_tc.cu), taken by launch_linear for bodies of >= 64 rows
 bool linear_tc_eligible(int rows, int N, int K);
 // split-K route for narrow outputs at few rows: `splits` f32 partials [split][rows][N] in ws, which

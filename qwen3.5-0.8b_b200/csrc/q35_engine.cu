@@ -1039,6 +1039,10 @@ extern "C" int q35_mtp_verify_k(q35_engine* e, q35_state* s, q35_mtp_state* m, c
 // ------------------------------------------------------------------------------------------------
 // single stages
 // ------------------------------------------------------------------------------------------------
+extern "C" const char* q35_op_linear_route(int rows, int N, int K, int epilogue) {
+    return linear_route(rows, N, K, epilogue == 1 ? EPI_SWIGLU : (epilogue == 2 ? EPI_ARGMAX : EPI_PLAIN));
+}
+
 extern "C" int q35_engine_launch_count(q35_engine* e, long long* count_host) {
     REQUIRE(e && count_host, Q35_ERR_ARG, "q35_engine_launch_count: null argument");
     *count_host = e->n_launch;
@@ -1072,6 +1076,40 @@ extern "C" int q35_op_linear_norm(q35_engine* e, const uint16_t* resid, const ui
     CK(launch_linear_norm_rows(resid, nw, W, out, rows, N, swiglu ? EPI_SWIGLU : EPI_PLAIN, nullptr, 0,
                                static_cast<cudaStream_t>(stream)));
     return Q35_OK;
+}
+
+// The output / down projection stage exactly as a body runs it: resid <- bf16(resid + bf16(x . W^T)) and, above
+// 16 rows, normed = N(resid; nw) by the add + norm kernel (at most 16 rows: the next projection applies the norm).
+extern "C" int q35_op_proj_residual(q35_engine* e, const uint16_t* x, const uint16_t* W, uint16_t* resid,
+                                    const uint16_t* nw, uint16_t* normed, int rows, int K, void* stream) {
+    REQUIRE(e && x && W && resid && nw && normed, Q35_ERR_ARG, "q35_op_proj_residual: null argument");
+    REQUIRE(rows >= 1 && rows <= e->max_rows, Q35_ERR_CAPACITY, "q35_op_proj_residual: rows = %d, the engine holds %d", rows, e->max_rows);
+    REQUIRE(K == 2048 || K == 3584, Q35_ERR_ARG, "q35_op_proj_residual: K = %d unsupported", K);
+    REQUIRE(aligned16(x) && aligned16(W) && aligned16(resid) && aligned16(nw) && aligned16(normed), Q35_ERR_ARG,
+            "q35_op_proj_residual: pointers must be 16-byte aligned");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    pdl_set_rows(rows);
+    if (body_fused(e, rows)) {
+        CK(launch_linear_resid_rows(x, W, resid, rows, K, nullptr, 0, st));
+        return Q35_OK;
+    }
+    const int sp = linear_tc_splits(rows, kHidden, K, kSplitMaxRows);
+    if (sp > 1) {
+        CK(launch_linear_tc_split(x, W, e->split_ws, rows, kHidden, K, sp, e->dev_status, st));
+        CK(launch_add_norm(resid, nullptr, nullptr, 0, nullptr, nw, resid, normed, rows, st, e->split_ws, sp));
+    } else {
+        CK(launch_linear(x, W, e->delta, rows, kHidden, K, EPI_PLAIN, nullptr, nullptr, nullptr, st, e->dev_status));
+        CK(launch_add_norm(resid, nullptr, nullptr, 0, e->delta, nw, resid, normed, rows, st));
+    }
+    return Q35_OK;
+}
+extern "C" const char* q35_op_proj_residual_route(q35_engine* e, int rows, int K) {
+    if (e == nullptr) return "unsupported";
+    if (body_fused(e, rows)) return "gemv_rows_kernel (residual epilogue)";
+    if (linear_tc_splits(rows, kHidden, K, kSplitMaxRows) > 1) return "gemm_tc_kernel<128,4> split-K + add_norm_split_kernel";
+    static thread_local char buf[160];
+    snprintf(buf, sizeof(buf), "%s + add_norm_kernel", linear_route(rows, kHidden, K, EPI_PLAIN));
+    return buf;
 }
 
 // One block of the decoder in isolation, for layer-level teacher forcing: x_in [lanes*T][1024] are the
@@ -1111,6 +1149,7 @@ extern "C" int q35_op_linear(const uint16_t* x, const uint16_t* W, uint16_t* out
     REQUIRE(N >= 8 && N % 8 == 0, Q35_ERR_ARG, "q35_op_linear: N = %d must be a multiple of 8", N);
     REQUIRE(K == 1024 || K == 2048 || K == 3584, Q35_ERR_ARG, "q35_op_linear: K = %d unsupported", K);
     REQUIRE(aligned16(x) && aligned16(W) && aligned16(out), Q35_ERR_ARG, "q35_op_linear: pointers must be 16-byte aligned");
+    pdl_set_rows(rows);
     CK(launch_linear(x, W, out, rows, N, K, EPI_PLAIN, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream)));
     return Q35_OK;
 }
@@ -1123,12 +1162,14 @@ extern "C" int q35_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16
 
 extern "C" int q35_op_mlp_gateup(const uint16_t* x, const uint16_t* Wgu, uint16_t* act, int rows, void* stream) {
     REQUIRE(x && Wgu && act && rows >= 1 && aligned16(x) && aligned16(Wgu) && aligned16(act), Q35_ERR_ARG, "q35_op_mlp_gateup: bad argument");
+    pdl_set_rows(rows);
     CK(launch_linear(x, Wgu, act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream)));
     return Q35_OK;
 }
 
 extern "C" int q35_op_lm_head(q35_engine* e, const uint16_t* x, int rows, int* tokens, float* logits_f32, void* stream) {
     REQUIRE(e && x && tokens && rows >= 1 && aligned16(x), Q35_ERR_ARG, "q35_op_lm_head: bad argument");
+    pdl_set_rows(rows);
     return run_head(e, x, rows, tokens, logits_f32, static_cast<cudaStream_t>(stream));
 }
 
@@ -1155,6 +1196,7 @@ extern "C" int q35_op_gdn_step(uint16_t* proj, const uint16_t* conv_w, const uin
     gp.proj = proj; gp.conv_w = conv_w; gp.A_log = A_log; gp.dt_bias = dt_bias; gp.norm_w = norm_w;
     gp.S[0] = S; gp.win[0] = window; gp.sel = nullptr;      // GdnParams gp{} left the shadow buffers null
     gp.y = y; gp.lanes = lanes; gp.T = T; gp.checkpoint = 0;
+    pdl_set_rows(lanes * T);
     if (T >= kGdnChunkMinT)
         CK(launch_gdn_chunked(gp, static_cast<cudaStream_t>(stream)));
     else

@@ -568,6 +568,17 @@ static cudaError_t dispatch(const uint16_t* x, const uint16_t* W, void* out, int
     return run_tiled<32, 128, 1, 8, 4, EPI>(x, W, out, M, N, K, partials, logits, n_parts, st);
 }
 
+// which kernel launch_linear picks for a shape (the same conditions, in the same order)
+const char* linear_route(int rows, int N, int K, int epi) {
+    if (rows <= 0 || N <= 0 || (N & 7) || (K != 1024 && K != 2048 && K != 3584)) return "unsupported";
+    if (linear_tc_eligible(rows, N, K) || (epi == EPI_ARGMAX && head_tc_few_rows() && N >= 128 && K % 64 == 0)) {
+        if (epi == EPI_PLAIN && linear_tc_splits(rows, N, K, kSplitMaxRows) > 1) return "gemm_tc_kernel<128,4> split-K + add_norm_split_kernel";
+        return linear_tc_route(rows, N, epi);
+    }
+    if (rows <= 16) return "gemv_rows_kernel";
+    return "gemm_tiled_kernel (mma.sync)";
+}
+
 cudaError_t launch_linear(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K,
                           int epi, ArgMax* partials, float* logits, int* n_parts_out, cudaStream_t st,
                           int* status) {

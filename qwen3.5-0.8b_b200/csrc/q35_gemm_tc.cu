@@ -542,6 +542,16 @@ cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* 
     return run_tc<128, 4, EPI_PARTIAL>(x, W, ws, rows, N, K, splits, nullptr, nullptr, 0, status, st);
 }
 
+// name of the tcgen05 form launch_linear_tc takes (for the benchmark's per-shape report)
+const char* linear_tc_route(int rows, int N, int epi) {
+    const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
+    if (use_persist(rows, N)) return "gemm_tc_persist_kernel (128x256 tiles, persistent)";
+    if (epi == EPI_ARGMAX) return "gemm_tc_kernel<128,3>";
+    if (tiles < 100) return "gemm_tc_kernel<64,8>";
+    if (tiles <= sm_count()) return "gemm_tc_kernel<128,6>";
+    return "gemm_tc_kernel<128,3>";
+}
+
 cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
                              ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
     const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);

@@ -69,7 +69,8 @@ EXPORTS = [
     "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
     "q35_lm_head_argmax_static", "q35_engine_clear_status", "q35_engine_launch_count",
-    "q35_mtp_draft_taps", "q35_op_linear_resid", "q35_op_linear_norm", "q35_op_layer",
+    "q35_mtp_draft_taps", "q35_op_linear_resid", "q35_op_linear_norm", "q35_op_layer", "q35_op_linear_route",
+    "q35_op_proj_residual", "q35_op_proj_residual_route",
 ]
 
 _lib = None
@@ -96,8 +97,7 @@ def load_library() -> C.CDLL:
     lib.q35_last_error.restype = C.c_char_p
     for name in EXPORTS:
         fn = getattr(lib, name)          # AttributeError = symbol not exported
-        if name != "q35_last_error":
-            fn.restype = C.c_int
+        fn.restype = C.c_char_p if name in ("q35_last_error", "q35_op_linear_route", "q35_op_proj_residual_route") else C.c_int
     _lib = lib
     return lib
 
@@ -465,6 +465,21 @@ class Engine:
                                            _ptr(u), _ptr(xd), _ptr(lg), _stream()))
         return prop, u, xd, lg
 
+    def op_proj_residual(self, x, Wt, resid, nw, normed=None):
+        """Output / down projection stage as a body runs it: resid updated in place, normed written above 16 rows."""
+        if normed is None:
+            normed = torch.empty_like(resid)
+        _check(self.lib.q35_op_proj_residual(self.handle, _ptr(x), _ptr(Wt), _ptr(resid), _ptr(nw), _ptr(normed),
+                                             x.shape[0], Wt.shape[1], _stream()))
+        return resid, normed
+
+    def op_proj_residual_route(self, rows: int, K: int) -> str:
+        return self.lib.q35_op_proj_residual_route(self.handle, rows, K).decode()
+
+    def op_linear_route(self, rows: int, N: int, K: int, epilogue: int = 0) -> str:
+        """Kernel a projection of this shape is routed to (0 plain, 1 SwiGLU, 2 head + argmax)."""
+        return self.lib.q35_op_linear_route(rows, N, K, epilogue).decode()
+
     def op_mlp_gateup(self, x, Wgu):
         act = torch.empty((x.shape[0], W.D_FF), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.q35_op_mlp_gateup(_ptr(x), _ptr(Wgu), _ptr(act), x.shape[0], _stream()))
@@ -551,9 +566,17 @@ class MtpRoundGraph:
     worst case per replay (depth + 1 positions, depth draft rows); `state.sync_bound()` /
     `mtp.sync_bound()` tighten them when the caller synchronises anyway."""
 
-    def __init__(self, engine: Engine, state: LaneState, mtp: MtpState, depth: int = 1, history: int = 0):
+    def __init__(self, engine: Engine, state: LaneState, mtp: MtpState, depth: int = 1, history: int = 0,
+                 forced_tokens: torch.Tensor | None = None):
+        """forced_tokens (int32 [lanes, n], optional): the lanes' true greedy continuations (token i of a
+        lane = the i-th token after the one seeded into `tok`).  The drafts still run, but the verifier is
+        handed forced_tokens[lane, emitted so far ...] as candidates, so every candidate that is the
+        target's own next token is accepted: the accept branch of a round can be timed on weights whose
+        draft never agrees with the target."""
         L = state.lanes
         self.engine, self.state, self.mtp, self.depth = engine, state, mtp, depth
+        self.forced = forced_tokens
+        self.emitted_lane = torch.zeros(L, dtype=torch.int64, device="cuda")     # tokens emitted per lane by the replays
         # optional ring of the last `history` rounds' verdicts, written by the graph itself (slot = rounds % history),
         # for a caller that reads verdicts back every few rounds without launching anything between replays
         self.history = history
@@ -571,10 +594,18 @@ class MtpRoundGraph:
             pos = (state.positions + 1).int()
             if depth == 1:
                 d = engine.mtp_draft(mtp, self.h, self.tok, pos)
-                _, _, h_next = engine.mtp_verify(state, mtp, self.tok, d, emit=self.emit, n_emit=self.n_emit)
             else:
                 d = engine.mtp_draft_k(mtp, self.h, self.tok, pos, depth)
+            if forced_tokens is not None:
+                idx = (self.emitted_lane[:, None] + torch.arange(depth, device="cuda")[None]).clamp_(max=forced_tokens.shape[1] - 1)
+                d = forced_tokens.gather(1, idx).to(torch.int32).reshape(L, depth).contiguous()
+                if depth == 1:
+                    d = d[:, 0].contiguous()
+            if depth == 1:
+                _, _, h_next = engine.mtp_verify(state, mtp, self.tok, d, emit=self.emit, n_emit=self.n_emit)
+            else:
                 _, _, h_next = engine.mtp_verify_k(state, mtp, self.tok, d, emit=self.emit, n_emit=self.n_emit)
+            self.emitted_lane += self.n_emit
             self.tok.copy_(self.emit.gather(1, (self.n_emit - 1).long()[:, None])[:, 0])
             self.h.copy_(h_next)
             self.emitted_total += self.n_emit.sum()

@@ -166,6 +166,23 @@ def test_fused_residual_stream_matches_add_norm_kernels(eng):
         assert rel_l2(normed.float().cpu(), n_ref.float().cpu()) < 3e-3
 
 
+@pytest.mark.parametrize("rows", [3, 16, 17, 40, 130, 300, 600])
+def test_proj_residual_stage(eng, rows):
+    """The output / down projection stage as a body runs it (fused few-row kernel, K-split tensor-core tiles
+    summed by the add + norm kernel, or plain tiles + add + norm) against the same composition in torch."""
+    for K in (2048, 3584):
+        g = torch.Generator().manual_seed(K + 3 * rows)
+        x = torch.randn((rows, K), generator=g).to(torch.bfloat16)
+        Wt = (torch.randn((1024, K), generator=g) * 0.02).to(torch.bfloat16)
+        r0 = torch.randn((rows, 1024), generator=g).to(torch.bfloat16)
+        nw = (torch.randn(1024, generator=g) * 0.1).to(torch.bfloat16)
+        resid, normed = eng.op_proj_residual(cu(x), cu(Wt), cu(r0.clone()), cu(nw))
+        ref = r0 + (x.double() @ Wt.double().t()).float().to(torch.bfloat16)
+        assert rel_l2(resid.float().cpu(), ref.float()) < 2e-3, (rows, K, eng.op_proj_residual_route(rows, K))
+        if rows > 16:
+            assert rel_l2(normed.float().cpu(), O.norm_zc(resid.cpu(), nw).float()) < 3e-3
+
+
 @pytest.mark.parametrize("rows", [1999, 4032])
 def test_linear_many_rows(eng, rows):
     """Bodies of thousands of rows (two or more waves of 128 x 256 tiles: the persistent tensor-core
