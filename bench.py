@@ -25,8 +25,8 @@ Reported on ONE JSON line by rank 0:
              (the two kernel-level configurations of the benchmark), N = 1 only;
   mtp        speculative rounds (draft + verify), reject path and forced-accept path.
 `--impl reference` times the CPU path alone in the same format.
-`--only-slice gdn:LANES` runs three launches of the recurrence kernel on one layer and exits (the
-small case a profiler capture of that kernel uses).
+`--only-slice gdn:LANES | head:ROWS | gemv:ROWS` runs a few launches of one kernel and exits (the small
+cases the profiler captures of those kernels use).
 """
 from __future__ import annotations
 
@@ -539,7 +539,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mtp", action="store_true", help="skip the MTP (configs[4]) section")
     ap.add_argument("--no-slices", action="store_true", help="skip the projection / recurrence slices (configs[1], configs[2])")
-    ap.add_argument("--only-slice", default="", help="gdn:LANES - three launches of the recurrence kernel on one layer, then exit")
+    ap.add_argument("--only-slice", default="", help="gdn:LANES | head:ROWS | gemv:ROWS - a few launches of one kernel, then exit (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -570,16 +570,36 @@ def main():
     pkg.build_lib.build()
 
     if args.only_slice:
-        kind, lanes_s = args.only_slice.split(":")
-        assert kind == "gdn"
-        eng = pkg.Engine(pkg.weights.make_weights(seed=0, vocab=16384), max_rows=64, vocab=16384, mtp=False)
-        L = int(lanes_s)
-        P, bufs = gdn_inputs(eng, L, 3, torch.Generator(device="cuda").manual_seed(12))
-        for S, win, proj in bufs:
-            eng.op_gdn_step(proj, P["conv"], P["A_log"], P["dt_bias"], P["norm"], S, win, L, 1)
+        # small cases for a profiler capture of ONE kernel: a few launches, each on its own operands, then exit
+        kind, n_s = args.only_slice.split(":")
+        n = int(n_s)
+        gen = torch.Generator(device="cuda").manual_seed(12)
+        if kind == "head":
+            eng = pkg.Engine(pkg.weights.make_weights(seed=0), max_rows=max(n, 64), mtp=False)
+            x = torch.randn((n, 1024), device="cuda", generator=gen).to(torch.bfloat16)
+            for _ in range(3):
+                eng.op_lm_head(x)
+            nbytes = 2 * eng.vocab * 1024
+        else:
+            eng = pkg.Engine(pkg.weights.make_weights(seed=0, vocab=16384), max_rows=max(n, 64), vocab=16384, mtp=False)
+            if kind == "gdn":
+                P, bufs = gdn_inputs(eng, n, 3, gen)
+                for S, win, proj in bufs:
+                    eng.op_gdn_step(proj, P["conv"], P["A_log"], P["dt_bias"], P["norm"], S, win, n, 1)
+                nbytes = n * GDN_BYTES_PER_LANE_LAYER
+            elif kind == "gemv":
+                # the GDN in-projection shape (8,224 x 1,024) at n <= 16 rows: the weight-streaming kernel
+                assert n <= 16
+                x = torch.randn((n, 1024), device="cuda", generator=gen).to(torch.bfloat16)
+                pool = [(torch.randn((8224, 1024), device="cuda", generator=gen) * 0.02).to(torch.bfloat16) for _ in range(24)]
+                for W in pool:
+                    eng.op_linear(x, W)
+                nbytes = 2 * 8224 * 1024
+            else:
+                raise SystemExit(f"unknown slice {kind}")
         torch.cuda.synchronize()
         assert eng.status() == 0
-        print(json.dumps({"only_slice": "gdn", "lanes": L, "launches": 3, "bytes_per_launch": L * GDN_BYTES_PER_LANE_LAYER}))
+        print(json.dumps({"only_slice": kind, "rows_or_lanes": n, "bytes_per_launch": nbytes}))
         return
 
     dist = world > 1
