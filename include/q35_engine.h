@@ -304,7 +304,9 @@ int q35_op_lm_head(q35_engine* e, const uint16_t* x, int rows, int* tokens, floa
  *   x [rows][1024] bf16, embed [vocab][1024] bf16, tokens [rows] int32; rows <= 16,
  *   vocab <= 262,144 and a multiple of 8 - larger sizes are refused with Q35_ERR_CAPACITY.
  * The first call on each device looks up the array's device address (with that device current);
- * make that first call before starting any stream capture.  All calls share the one array: two
+ * make that first call before starting any stream capture, and do not let two first calls on the same
+ * device run concurrently from two host threads (both would store the same address, but the look-up
+ * itself is not meant to be raced).  All calls share the one array: two
  * calls that may overlap on the GPU (different streams, no dependency) race on it.  Calls never
  * allocate or free: no cudaMalloc / cudaFree, and no library routine that allocates. */
 int q35_lm_head_argmax_static(const uint16_t* x, const uint16_t* embed, int vocab, int rows,
