@@ -25,7 +25,7 @@ Reported on ONE JSON line by rank 0:
              (the two kernel-level configurations of the benchmark), N = 1 only;
   mtp        speculative rounds (draft + verify), reject path and forced-accept path.
 `--impl reference` times the CPU path alone in the same format.
-`--only-slice gdn:LANES | head:ROWS | gemv:ROWS` runs a few launches of one kernel and exits (the small
+`--only-slice gdn:LANES | chunk:LANES | head:ROWS | gemv:ROWS` runs a few launches of one kernel and exits (the small
 cases the profiler captures of those kernels use).
 """
 from __future__ import annotations
@@ -539,7 +539,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-mtp", action="store_true", help="skip the MTP (configs[4]) section")
     ap.add_argument("--no-slices", action="store_true", help="skip the projection / recurrence slices (configs[1], configs[2])")
-    ap.add_argument("--only-slice", default="", help="gdn:LANES | head:ROWS | gemv:ROWS - a few launches of one kernel, then exit (profiler captures)")
+    ap.add_argument("--only-slice", default="", help="gdn:LANES | chunk:LANES | head:ROWS | gemv:ROWS - a few launches of one kernel, then exit (profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -587,6 +587,14 @@ def main():
                 for S, win, proj in bufs:
                     eng.op_gdn_step(proj, P["conv"], P["A_log"], P["dt_bias"], P["norm"], S, win, n, 1)
                 nbytes = n * GDN_BYTES_PER_LANE_LAYER
+            elif kind == "chunk":
+                # the chunk-64 prefill scan: n lanes x 64 tokens of one GDN layer (conv pass + scan kernel per launch)
+                P, bufs = gdn_inputs(eng, n, 1, gen)
+                S, win, _ = bufs[0]
+                for _ in range(3):
+                    proj = torch.randn((n * 64, 8224), device="cuda", generator=gen).to(torch.bfloat16)
+                    eng.op_gdn_step(proj, P["conv"], P["A_log"], P["dt_bias"], P["norm"], S, win, n, 64)
+                nbytes = n * (2 * 1048576 + 64 * 4 * 256 + 64 * 256)
             elif kind == "gemv":
                 # the GDN in-projection shape (8,224 x 1,024) at n <= 16 rows: the weight-streaming kernel
                 assert n <= 16

@@ -363,10 +363,12 @@ def test_gdn_chunked_vs_oracle(eng, weights, lanes, T):
         assert rel_l2(y[i * T:(i + 1) * T].float(), d["y"].float()) <= 1e-2
 
 
-def test_gdn_chunked_tensor_pipe_matches_simt_form(eng, weights, monkeypatch):
-    """The scan on the tensor pipe (split-TF32 products, blocked solve) against the f32 SIMT form of
-    the same chunk algebra on the same inputs, 3 lanes x 130 rows (two full chunks + a ragged one):
-    states within 2e-5 relative, identical conv windows, gated rows within the bf16 band."""
+def test_gdn_chunked_tcgen05_matches_warp_mma_form(eng, weights, monkeypatch):
+    """The scan's two forms on the same inputs, 3 lanes x 130 rows (two full chunks + a ragged one): the two large
+    products on tcgen05 with bf16 x 3 operand pieces and tensor-memory accumulators (the default) against every
+    product on warp-level mma with split-TF32 operands.  Both carry f32-grade operands (~2^-20 per product), so the
+    states agree to 2e-5 relative, the conv windows are identical and the gated rows sit within the bf16 band.
+    (Both are also held to 1e-4 of the reference's state by the golden and oracle tests above.)"""
     l, lanes, T = 1, 3, 130
     gen = torch.Generator().manual_seed(77)
     h = torch.randn((lanes, T, 1024), generator=gen).to(torch.bfloat16)
@@ -374,17 +376,18 @@ def test_gdn_chunked_tensor_pipe_matches_simt_form(eng, weights, monkeypatch):
     S0 = torch.randn((lanes, 16, 128, 128), generator=gen) * 0.1
     proj = torch.stack([gdn_proj_rows(weights, l, h[i]) for i in range(lanes)]).reshape(lanes * T, -1)
     out = {}
-    for form in ("simt", "tc"):
+    for form in ("mma", "umma"):
         monkeypatch.setenv("Q35_GDN_CHUNK", form)
         out[form] = gdn_device_step(eng, weights, l, proj.clone(), S0, win, lanes, T)
-    (y_a, S_a, w_a), (y_b, S_b, w_b) = out["simt"], out["tc"]
+    (y_a, S_a, w_a), (y_b, S_b, w_b) = out["mma"], out["umma"]
     e_s = rel_l2(S_b, S_a)
     e_y = rel_l2(y_b.float(), y_a.float())
-    note("gdn_chunk_tensor_pipe_vs_simt", [e_s, e_y])
+    note("gdn_chunk_tcgen05_vs_warp_mma", [e_s, e_y])
     assert e_s <= 2e-5, e_s
     assert torch.equal(w_a, w_b)
     assert e_y <= 4e-3, e_y
     assert not torch.equal(S_a, S0)                     # the scan did move the state
+    assert eng.status() == 0
 
 
 # ------------------------------------------------------------------------------------- attention
