@@ -255,6 +255,11 @@ int q35_op_add_norm(const uint16_t* x, const uint16_t* delta, const uint16_t* w,
                     uint16_t* sum_out, uint16_t* normed_out, int rows, void* stream);
 /* proj_rows (engine/kernels.h:183-297): out [rows][N] = bf16(x [rows][K] . W[N][K]^T).
  * K in {1024, 2048, 3584}; N a multiple of 8. */
+/* The stage entry points that take no engine (q35_op_linear, q35_op_mlp_gateup) report a bounded device
+ * wait that ran out through a status word of the library itself: synchronises the device, reads the word
+ * (0 = healthy, codes as for q35_engine_status) and clears it.  Unlike the engine's word it does not make
+ * later kernels skip their work. */
+int q35_ops_status(int* status_host);
 int q35_op_linear(const uint16_t* x, const uint16_t* W, uint16_t* out, int rows, int N, int K,
                   void* stream);
 /* The fused residual stream of bodies of at most 16 rows, as two stages (the reference's pairing of

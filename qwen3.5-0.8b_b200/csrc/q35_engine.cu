@@ -1143,6 +1143,31 @@ extern "C" int q35_op_add_norm(const uint16_t* x, const uint16_t* delta, const u
     return Q35_OK;
 }
 
+// The stage entry points that take no engine report a bounded wait that ran out through this word of the
+// library image (one per device that loads the library); q35_ops_status reads and clears it.
+static __device__ int g_ops_status;
+static int* ops_status_ptr() {
+    static int* ptr[kMaxDevices] = {nullptr};        // every writer stores the same address
+    const int dev = current_device_slot();
+    if (dev < 0) return nullptr;
+    if (ptr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_ops_status) != cudaSuccess) return nullptr;
+        ptr[dev] = static_cast<int*>(p);
+    }
+    return ptr[dev];
+}
+
+extern "C" int q35_ops_status(int* status_host) {
+    REQUIRE(status_host, Q35_ERR_ARG, "q35_ops_status: null argument");
+    int* d = ops_status_ptr();
+    REQUIRE(d != nullptr, Q35_ERR_CUDA, "q35_ops_status: no current device");
+    CK(cudaDeviceSynchronize());
+    CK(cudaMemcpy(status_host, d, sizeof(int), cudaMemcpyDeviceToHost));
+    if (*status_host != 0) CK(cudaMemset(d, 0, sizeof(int)));
+    return Q35_OK;
+}
+
 extern "C" int q35_op_linear(const uint16_t* x, const uint16_t* W, uint16_t* out, int rows, int N, int K,
                              void* stream) {
     REQUIRE(x && W && out && rows >= 1, Q35_ERR_ARG, "q35_op_linear: bad argument");
@@ -1150,7 +1175,7 @@ extern "C" int q35_op_linear(const uint16_t* x, const uint16_t* W, uint16_t* out
     REQUIRE(K == 1024 || K == 2048 || K == 3584, Q35_ERR_ARG, "q35_op_linear: K = %d unsupported", K);
     REQUIRE(aligned16(x) && aligned16(W) && aligned16(out), Q35_ERR_ARG, "q35_op_linear: pointers must be 16-byte aligned");
     pdl_set_rows(rows);
-    CK(launch_linear(x, W, out, rows, N, K, EPI_PLAIN, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream)));
+    CK(launch_linear(x, W, out, rows, N, K, EPI_PLAIN, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), ops_status_ptr()));
     return Q35_OK;
 }
 
@@ -1163,7 +1188,7 @@ extern "C" int q35_pack_gate_up(const uint16_t* gate, const uint16_t* up, uint16
 extern "C" int q35_op_mlp_gateup(const uint16_t* x, const uint16_t* Wgu, uint16_t* act, int rows, void* stream) {
     REQUIRE(x && Wgu && act && rows >= 1 && aligned16(x) && aligned16(Wgu) && aligned16(act), Q35_ERR_ARG, "q35_op_mlp_gateup: bad argument");
     pdl_set_rows(rows);
-    CK(launch_linear(x, Wgu, act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream)));
+    CK(launch_linear(x, Wgu, act, rows, 2 * kFF, kHidden, EPI_SWIGLU, nullptr, nullptr, nullptr, static_cast<cudaStream_t>(stream), ops_status_ptr()));
     return Q35_OK;
 }
 

@@ -69,7 +69,7 @@ EXPORTS = [
     "q35_op_add_norm", "q35_op_linear",
     "q35_pack_gate_up", "q35_op_mlp_gateup", "q35_op_lm_head", "q35_op_gdn_step", "q35_op_attn_decode",
     "q35_lm_head_argmax_static", "q35_engine_clear_status", "q35_engine_launch_count",
-    "q35_mtp_draft_taps", "q35_op_linear_resid", "q35_op_linear_norm", "q35_op_layer", "q35_op_linear_route",
+    "q35_mtp_draft_taps", "q35_ops_status", "q35_op_linear_resid", "q35_op_linear_norm", "q35_op_layer", "q35_op_linear_route",
     "q35_op_proj_residual", "q35_op_proj_residual_route",
 ]
 
@@ -434,6 +434,12 @@ class Engine:
         out = torch.empty((2 * W.D_FF, W.D_MODEL), dtype=torch.bfloat16, device="cuda")
         _check(self.lib.q35_pack_gate_up(_ptr(gate), _ptr(up), _ptr(out), _stream()))
         return out
+
+    def ops_status(self) -> int:
+        """Status word of the stage entry points that take no engine (op_linear, op_mlp_gateup); cleared by the read."""
+        v = C.c_int(-1)
+        _check(self.lib.q35_ops_status(C.byref(v)))
+        return v.value
 
     def op_linear_resid(self, x, Wt, resid):
         """resid [rows, 1024] += x @ Wt.T in place (bf16 roundings of the reference); returns resid."""

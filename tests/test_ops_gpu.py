@@ -48,6 +48,7 @@ def eng(pkg, weights):
     e = pkg.Engine(weights, max_rows=4096)
     yield e
     assert e.status() == 0, "a kernel gave up a bounded wait"
+    assert e.ops_status() == 0, "a stage entry point without an engine gave up a bounded wait"
     e.close()
 
 
