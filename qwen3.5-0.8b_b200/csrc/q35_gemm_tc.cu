@@ -411,6 +411,225 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_c
     }
 }
 
+// ---- the tied head for bodies of at most 32 rows: the TABLE is the M operand --------------------------
+// logits^T [vocab][rows] = table [vocab][K] . x [rows][K]^T : A = 128 table rows of one k-block (K-major, by TMA),
+// B = the body's rows (N = NB = 16 or 32 columns of the MMA; rows past the body are zero-filled by TMA, once),
+// D = 128 lanes x NB columns of tensor memory, double-buffered.  The x rows for ALL of K (16 k-blocks x NB x 128 B) are
+// loaded once per CTA and stay, so a ring stage holds nothing but 16 KiB of the table and eleven (NB = 16) or nine
+// of them are in flight per SM (with 64 columns only five fit and the per-row reduction shows: 152 us; not built); the
+// form with x as the M operand moved a 16 KiB x tile of which at most one eighth was real through every stage and
+// did sixteen times the tensor-pipe work (116 -> 82 us per 1-row head = 6.2 TB/s).  Warp roles: 0 = TMA producer, 1 = tensor
+// memory owner + MMA issuer, 2..5 = epilogue: thread = one table row of the tile, its NB accumulator columns are the
+// logits of that token id for the body's rows; optional f32 logits stores (coalesced along the vocabulary), then per
+// body row a (value, lowest id) reduction over the warp's 32 ids by shuffles and over the four warps through shared
+// memory: one partial per (row, 128-id tile), as the other head forms write.
+constexpr int H_THREADS = 192, H_KB = 16, H_MAX_NB = 32;
+constexpr int head_stages(int nb) { return nb <= 16 ? 11 : 9; }
+constexpr size_t head_smem(int nb) { return (size_t)head_stages(nb) * A_BYTES + (size_t)H_KB * nb * 128 + 1024; }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+template <int H_NB>
+__global__ void __launch_bounds__(H_THREADS, 1)
+head_rows_tc_kernel(const __grid_constant__ CUtensorMap tma_x, const __grid_constant__ CUtensorMap tma_w, int M, int N,
+                    int n_tiles, ArgMax* __restrict__ partials, float* __restrict__ logits, int n_parts,
+                    int* __restrict__ status) {
+    static_assert(H_NB == 16 || H_NB == 32, "one body row per lane of an epilogue warp");
+    constexpr uint32_t IDESC = instr_desc(BM, H_NB);
+    constexpr int H_STAGES = head_stages(H_NB);
+    constexpr int H_XBYTES = H_KB * H_NB * 128;              // [k-block][NB rows][128 B]
+    constexpr uint32_t TMEM_COLS = 2 * H_NB < 32 ? 32 : 2 * H_NB;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long bars[2 * H_STAGES + 6];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+    __shared__ int issued_s, consumed_s, x_issued_s, x_waited_s;
+    __shared__ float wb_v[2][4][H_NB];
+    __shared__ int wb_i[2][4][H_NB];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) { prefetch_tensormap(&tma_w); prefetch_tensormap(&tma_x); }
+    const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t xs = ring + H_STAGES * A_BYTES;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[H_STAGES]);
+    const uint32_t accf0 = smem_u32(&bars[2 * H_STAGES]), acce0 = smem_u32(&bars[2 * H_STAGES + 2]);
+    const uint32_t xfull = smem_u32(&bars[2 * H_STAGES + 4]), drain = smem_u32(&bars[2 * H_STAGES + 5]);
+    const int first = blockIdx.x;
+    const int pre = first < n_tiles ? (H_KB < H_STAGES ? H_KB : H_STAGES) : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < H_STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        mbar_init(accf0, 1); mbar_init(accf0 + 8, 1);
+        mbar_init(acce0, 4); mbar_init(acce0 + 8, 4);
+        mbar_init(xfull, 1); mbar_init(drain, 1);
+        abort_s = 0; issued_s = 0; consumed_s = 0; x_issued_s = 0; x_waited_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        // table tiles of the first stages fly while the kernel that produces x is still running
+        for (int kb = 0; kb < pre; ++kb) {
+            mbar_expect_tx(full0 + 8 * kb, A_BYTES);
+            tma_load_2d(ring + kb * A_BYTES, &tma_w, kb * BK, first * BM, full0 + 8 * kb);
+        }
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();
+    const bool dead = status != nullptr && *status != 0;      // an earlier kernel gave up
+    const int my_last = dead ? (pre > 0 ? first + 1 : first) : n_tiles;   // a dead CTA only lets its copies land
+
+    if (warp == 0) {
+        if (lane == 0) {
+            if (!dead && first < n_tiles) {
+                mbar_expect_tx(xfull, H_XBYTES);
+                for (int kb = 0; kb < H_KB; ++kb) tma_load_2d(xs + kb * (H_NB * 128), &tma_x, kb * BK, 0, xfull);
+                x_issued_s = 1;
+            }
+            int it = 0;
+            bool ok = true;
+            for (int tile = first; tile < my_last && ok; tile += gridDim.x) {
+                const int kb_end = dead ? pre : H_KB;
+                for (int kb = 0; kb < kb_end; ++kb, ++it) {
+                    if (it < pre) continue;                   // issued ahead of the wait
+                    const int s = it % H_STAGES;
+                    if (!mbar_wait_or_abort(empty0 + 8 * s, ((it / H_STAGES) & 1) ^ 1, &abort_s)) {
+                        abort_s = 1; if (status) atomicExch(status, 2); ok = false; break;
+                    }
+                    mbar_expect_tx(full0 + 8 * s, A_BYTES);
+                    tma_load_2d(ring + s * A_BYTES, &tma_w, kb * BK, tile * BM, full0 + 8 * s);
+                }
+            }
+            issued_s = it;
+            pdl_trigger();               // every load of this CTA is issued: the successor may start
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int it = 0, i = 0;
+            bool ok = true;
+            if (!dead && first < n_tiles) {
+                if (!mbar_wait_or_abort(xfull, 0, &abort_s)) { abort_s = 1; if (status) atomicExch(status, 3); ok = false; }
+                else x_waited_s = 1;
+            }
+            for (int tile = first; tile < my_last && ok; tile += gridDim.x, ++i) {
+                const int buf = i & 1;
+                const uint32_t d_tmem = tmem_base + buf * H_NB;
+                if (!dead && !mbar_wait_or_abort(acce0 + 8 * buf, ((i >> 1) & 1) ^ 1, &abort_s)) {
+                    abort_s = 1; if (status) atomicExch(status, 5); ok = false; break;
+                }
+                tc_fence_after();
+                const int kb_end = dead ? pre : H_KB;
+                for (int kb = 0; kb < kb_end; ++kb, ++it) {
+                    const int s = it % H_STAGES;
+                    if (!mbar_wait_or_abort(full0 + 8 * s, (it / H_STAGES) & 1, &abort_s)) {
+                        abort_s = 1; if (status) atomicExch(status, 3); ok = false; break;
+                    }
+                    if (dead) continue;
+                    tc_fence_after();
+                    const uint32_t a = ring + s * A_BYTES, b = xs + kb * (H_NB * 128);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        tc_mma(d_tmem, smem_desc_sw128(a + k * 32), smem_desc_sw128(b + k * 32), IDESC, (kb | k) != 0 ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);           // frees the stage once these MMAs have read it
+                }
+                if (ok && !dead) tc_commit(accf0 + 8 * buf);
+            }
+            consumed_s = it;
+            if (!ok) {                                   // let the MMAs already issued finish before the memory goes
+                tc_commit(drain);
+                mbar_wait(drain, 0);
+            }
+        }
+    } else if (!dead) {
+        // ---- epilogue: thread = table row (tensor-memory lane) of the tile ----
+        const int q = warp & 3, ew = warp - 2;
+        int i = 0;
+        bool live = true;
+        for (int tile = first; tile < n_tiles; tile += gridDim.x, ++i) {
+            const int buf = i & 1;
+            // one outcome for the whole warp: tcgen05.ld below needs all 32 lanes
+            if (live && !__all_sync(0xffffffffu, mbar_wait_or_abort(accf0 + 8 * buf, (i >> 1) & 1, &abort_s))) {
+                if (lane == 0) { abort_s = 1; if (status) atomicExch(status, 4); }
+                live = false;
+            }
+            float myv = -INFINITY;
+            int myi = 0x7fffffff;
+            if (live) {
+                tc_fence_after();
+                const int n = tile * BM + q * 32 + lane;
+                const bool n_ok = n < N;
+#pragma unroll
+                for (int c = 0; c < H_NB / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + buf * H_NB + c * 16, r);
+                    if (c == H_NB / 16 - 1) {
+                        // this warp has read its part of the accumulator: hand the buffer back to the MMA thread
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acce0 + 8 * buf);
+                    }
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const int j = c * 16 + jj;
+                        if (j >= M) break;                 // M is the same for every thread
+                        const float v = __uint_as_float(r[jj]);
+                        if (logits != nullptr && n_ok) logits[(size_t)j * N + n] = v;
+                        float bv = n_ok ? v : -INFINITY;
+                        int bi = n_ok ? n : 0x7fffffff;
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+                            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                        }
+                        if (lane == j) { myv = bv; myi = bi; }      // lane j keeps the winner of body row j
+                    }
+                }
+            }
+            // the four warps' winners meet in shared memory (all four run this barrier for every tile of the CTA)
+            if (lane < H_NB) { wb_v[buf][ew][lane] = myv; wb_i[buf][ew][lane] = myi; }
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            const int et = ew * 32 + lane;                 // epilogue thread: one body row each
+            if (et < M && !abort_s) {
+                float bv = wb_v[buf][0][et];
+                int bi = wb_i[buf][0][et];
+#pragma unroll
+                for (int w = 1; w < 4; ++w) {
+                    const float ov = wb_v[buf][w][et];
+                    const int oi = wb_i[buf][w][et];
+                    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                }
+                partials[(size_t)et * n_parts + tile] = ArgMax{bv, bi};
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0 && abort_s) {
+        // copies issued but never consumed must land before the shared memory is given up
+        for (int k = consumed_s; k < issued_s; ++k) mbar_wait(full0 + 8 * (k % H_STAGES), (k / H_STAGES) & 1);
+        if (x_issued_s && !x_waited_s) mbar_wait(xfull, 0);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side: tensor maps -------------------------------------------------------------------
 // bf16 matrix [rows][K] row-major, box = 64 k-elements x box_rows rows, 128-byte swizzle, zero fill
 bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
@@ -453,6 +672,29 @@ cudaError_t run_tc_persist(const uint16_t* x, const uint16_t* W, void* out, int 
     const int total = m_tiles * n_tiles;
     return launch_k(kern, dim3(total < sms ? total : sms), dim3(P_THREADS), smem, st, mx, mw, out, M, N, K / BK,
                     m_tiles, n_tiles, partials, logits, n_parts, status);
+}
+
+// the head of at most 32 rows with the table as the M operand (Q35_HEAD_SWAP=0 keeps x as the M operand)
+bool head_rows_form(int rows, int N, int K, int epi) {
+    static int mode = -1;
+    if (mode < 0) {
+        const char* env = std::getenv("Q35_HEAD_SWAP");
+        mode = (env != nullptr && env[0] == '0') ? 0 : 1;
+    }
+    return mode == 1 && epi == EPI_ARGMAX && rows <= H_MAX_NB && K == H_KB * BK && N >= BM;
+}
+template <int NB>
+cudaError_t run_head_rows_tc(const uint16_t* x, const uint16_t* W, int M, int N, int K, int sms, ArgMax* partials,
+                             float* logits, int n_parts, int* status, cudaStream_t st) {
+    static bool attr_done[kMaxDevices] = {false};
+    cudaError_t e = opt_in_smem(head_rows_tc_kernel<NB>, head_smem(NB), attr_done);
+    if (e != cudaSuccess) return e;
+    CUtensorMap mx, mw;
+    if (!make_map(&mx, x, M, K, NB) || !make_map(&mw, W, N, K, BM)) return cudaErrorInvalidValue;
+    const int n_tiles = (N + BM - 1) / BM;
+    if (n_parts < n_tiles) return cudaErrorInvalidValue;
+    return launch_k(head_rows_tc_kernel<NB>, dim3(n_tiles < sms ? n_tiles : sms), dim3(H_THREADS), head_smem(NB), st, mx, mw,
+                    M, N, n_tiles, partials, logits, n_parts, status);
 }
 
 // the persistent form pays from about one wave of 128 x 256 tiles (Q35_GEMM_PERSIST_MIN overrides)
@@ -502,6 +744,7 @@ cudaError_t launch_linear_tc_split(const uint16_t* x, const uint16_t* W, float* 
 
 // name of the tcgen05 form launch_linear_tc takes (for the benchmark's per-shape report)
 const char* linear_tc_route(int rows, int N, int epi) {
+    if (head_rows_form(rows, N, H_KB * BK, epi)) return rows <= 16 ? "head_rows_tc_kernel<16> (table rows as the M operand, persistent)" : "head_rows_tc_kernel<32> (table rows as the M operand, persistent)";
     const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
     if (use_persist(rows, N)) return "gemm_tc_persist_kernel (128x256 tiles, persistent)";
     if (epi == EPI_ARGMAX) return "gemm_tc_kernel<128,3>";
@@ -512,6 +755,10 @@ const char* linear_tc_route(int rows, int N, int epi) {
 
 cudaError_t launch_linear_tc(const uint16_t* x, const uint16_t* W, void* out, int rows, int N, int K, int epi,
                              ArgMax* partials, float* logits, int n_parts, int* status, cudaStream_t st) {
+    if (head_rows_form(rows, N, K, epi)) {
+        if (rows <= 16) return run_head_rows_tc<16>(x, W, rows, N, K, sm_count(), partials, logits, n_parts, status, st);
+        return run_head_rows_tc<32>(x, W, rows, N, K, sm_count(), partials, logits, n_parts, status, st);
+    }
     const int tiles = ((rows + BM - 1) / BM) * ((N + 127) / 128);
     if (use_persist(rows, N)) {
         const int sms = sm_count();

@@ -233,7 +233,7 @@ def test_mlp_golden(eng, weights, golden):
 
 
 # ------------------------------------------------------------------------------------------- head
-@pytest.mark.parametrize("rows", [1, 4, 16, 17, 64, 130])
+@pytest.mark.parametrize("rows", [1, 4, 9, 16, 17, 32, 48, 64, 65, 130])
 def test_lm_head_argmax(eng, weights, rows):
     E = weights[O.LM + "embed_tokens.weight"]
     g = torch.Generator().manual_seed(rows + 11)
@@ -253,6 +253,29 @@ def test_lm_head_argmax(eng, weights, rows):
         if margin > 1e-2:
             assert int(tok[r]) == best
     note(f"lm_head_rows{rows}_rel_l2", err)
+
+
+@pytest.mark.parametrize("vocab", [1000, 4232])
+def test_lm_head_ragged_vocabulary(pkg, vocab):
+    """Vocabularies that are not a multiple of the 128 token ids a head tile owns: the last tile's rows past the
+    table are zero-filled and must stay out of the argmax, also when every real logit is negative; rows 1 to
+    64 take the forms with the table as the M operand (16, 32 or 64 columns), 65 rows the form with x as the M operand."""
+    p = pkg.weights.make_weights(seed=4, vocab=vocab)
+    E = p[O.LM + "embed_tokens.weight"]
+    e = pkg.Engine(p, max_rows=128)
+    for rows in (1, 7, 16, 17, 33, 64, 65):
+        g = torch.Generator().manual_seed(vocab + rows)
+        x = (torch.randn((rows, 1024), generator=g) * 2).to(torch.bfloat16)
+        x[0] = -E[vocab - 1] * 30                              # every logit of row 0 is <= 0 except by chance; the tail must not win with 0
+        tok, lg = e.op_lm_head(cu(x), want_logits=True)
+        ref = x.float() @ E.float().t()
+        assert rel_l2(lg.cpu(), ref) < 1e-4, (vocab, rows)
+        own = lg.cpu()
+        for r in range(rows):
+            assert 0 <= int(tok[r]) < vocab
+            assert int(tok[r]) == int((own[r] == own[r].max()).nonzero()[0]), (vocab, rows, r)
+    assert e.status() == 0
+    e.close()
 
 
 def test_lm_head_tie_goes_to_lowest_id(eng, weights):
