@@ -79,12 +79,12 @@ def test_add_norm_golden(eng, weights, golden):
 
 
 # ------------------------------------------------------------------------------------- projections
-SHAPES = [("in_proj_qkv", 6144, 1024), ("in_proj_z", 2048, 1024), ("in_proj_a", 16, 1024),
+SHAPES = [("in_proj_qkv", 6144, 1024), ("in_proj_z", 2048, 1024), ("in_proj_a", 16, 1024), ("gdn_in_grouped", 8224, 1024),
           ("out_proj", 1024, 2048), ("q_proj", 4096, 1024), ("k_proj", 512, 1024),
           ("down_proj", 1024, 3584)]
 
 
-@pytest.mark.parametrize("rows", [1, 2, 8, 9, 16, 17, 32, 33, 64, 128, 130, 512])
+@pytest.mark.parametrize("rows", [1, 2, 8, 9, 16, 17, 25, 32, 33, 64, 128, 130, 512])
 def test_linear_shapes(eng, rows):
     """The projection-slice shapes at ragged and tile-edge lane counts vs an f64 matmul of the
     same bf16 operands, rounded once to bf16."""
@@ -204,7 +204,7 @@ def test_linear_many_rows(eng, rows):
         note(f"linear_{name}_rows{rows}", err)
 
 
-@pytest.mark.parametrize("rows", [1, 5, 16, 17, 64, 100, 128, 300, 1999])
+@pytest.mark.parametrize("rows", [1, 5, 16, 17, 29, 32, 64, 100, 128, 300, 1999])
 def test_mlp_gateup_and_down(eng, weights, rows):
     pre = O.LM + "layers.0.mlp."
     g = torch.Generator().manual_seed(rows + 5)
