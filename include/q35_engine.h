@@ -131,7 +131,8 @@ int q35_engine_create(const q35_config* cfg, const q35_weights* w, void* stream,
 int q35_engine_destroy(q35_engine* e);
 int q35_step_census(const q35_engine* e, q35_census* out);
 /* Synchronises the device and reads the engine's status word: 0 = healthy; non-zero = a kernel gave
- * up a bounded wait (1 GDN tile fetch, 2-4 projection pipeline) and skipped its stores.  The
+ * up a bounded wait (1 GDN tile fetch, 2-5 tcgen05 projection / head pipeline, 5-6 attention page ring,
+ * 8 chunked prefill scan) and skipped its stores.  The
  * reference has no device-side waits; its nearest relative is the post-step
  * RequestState::check_invariants (engine/state.h:99). */
 int q35_engine_status(q35_engine* e, int* status_host);
