@@ -56,6 +56,7 @@ __device__ __forceinline__ void append_kv(const AttnParams& p, const uint16_t* _
 // row's K/V is in the cache before any row's scores are taken.
 __global__ void __launch_bounds__(64) attn_append_kernel(AttnParams p) {
     pdl_wait();
+    pdl_trigger();          // the attention kernel behind this one reads the cache only after its own wait
     const int row = blockIdx.x, kvh = blockIdx.y;
     const int lane_id = row / p.T, t = row % p.T;
     const int slot = p.slot[lane_id] + t;
@@ -250,6 +251,7 @@ attn_tma_kernel(AttnParams p, int ctx_pad, const __grid_constant__ CUtensorMap k
     __shared__ __align__(8) unsigned long long bars[2 * kRing];
     if (threadIdx.x == 0) { prefetch_tensormap(&kmap); prefetch_tensormap(&vmap); }
     pdl_wait();
+    pdl_trigger();          // the output projection behind this kernel may start fetching its weights
     if (p.status != nullptr && *p.status != 0) return;
 
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -481,6 +483,7 @@ attn_cluster_kernel(AttnParams p, int ctx_pad, int lpad, int cs, const __grid_co
     __shared__ float ml_s[8];                              // local max [4 heads] | local sum of exp [4]
     __shared__ __align__(16) float o_part[4 * kHeadDim];   // this CTA's f32 partial of P.V
     pdl_wait();
+    pdl_trigger();          // the output projection behind this kernel may start fetching its weights
     const bool dead = p.status != nullptr && *p.status != 0;
 
     const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;

@@ -145,16 +145,22 @@ static void free_all(std::vector<void*>& owner) {
 // body ids of a verify round: row (lane, 0) = cur, rows (lane, 1..k) = the lane's candidates
 __global__ void verify_ids_kernel(const int* __restrict__ cur, const int* __restrict__ cand, int k,
                                   int* __restrict__ out, int lanes) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= lanes * (k + 1)) return;
     const int lane_id = i / (k + 1), j = i % (k + 1);
     out[i] = j == 0 ? cur[lane_id] : cand[lane_id * k + j - 1];
 }
 __global__ void add_const_kernel(const int* __restrict__ in, int c, int* __restrict__ out, int n) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = in[i] + c;
 }
 __global__ void scatter_col_kernel(const int* __restrict__ in, int* __restrict__ out, int stride, int col, int n) {
+    pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[(size_t)i * stride + col] = in[i];
 }
@@ -170,6 +176,8 @@ __global__ void mtp_verdict_kernel(const int* __restrict__ cand, const int* __re
                                    int* __restrict__ n_emit, uint16_t* __restrict__ h_next,
                                    int* __restrict__ pos, int* __restrict__ sel,
                                    int* __restrict__ mtp_n, int lanes) {
+    pdl_wait();
+    pdl_trigger();          // the next round's first kernel may be set up; it reads what this one writes only after its own wait
     const int lane_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int ln = threadIdx.x & 31;
     if (lane_id >= lanes) return;
@@ -988,12 +996,10 @@ extern "C" int q35_mtp_draft_k(q35_engine* e, q35_mtp_state* m, const uint16_t* 
     for (int j = 0; j < k; ++j) {
         int rc = draft_once(e, m, h, y, p, m->prop_tmp, st);
         if (rc != Q35_OK) return rc;
-        scatter_col_kernel<<<(L + 255) / 256, 256, 0, st>>>(m->prop_tmp, proposals, k, j, L);
-        CK(cudaGetLastError());
+        CK(launch_k(scatter_col_kernel, dim3((L + 255) / 256), dim3(256), 0, st, m->prop_tmp, proposals, k, j, L));
         if (j + 1 < k) {
             CK(copy_rows(m->h_tmp, e->normed, (size_t)L * kHidden, st));
-            add_const_kernel<<<(L + 255) / 256, 256, 0, st>>>(pos, j + 1, m->pos_tmp, L);
-            CK(cudaGetLastError());
+            CK(launch_k(add_const_kernel, dim3((L + 255) / 256), dim3(256), 0, st, pos, j + 1, m->pos_tmp, L));
             // prop_tmp is read by the next pass's first kernel and rewritten by its last: stream order suffices
             h = m->h_tmp; y = m->prop_tmp; p = m->pos_tmp;
         }
@@ -1007,15 +1013,13 @@ static int verify_round(q35_engine* e, q35_state* s, q35_mtp_state* m, const int
     // a rejecting round drops k rows from the draft cache: they must have been drafted since the last round
     REQUIRE(m->drafts_pending >= k, Q35_ERR_STATE, "verify of depth %d after %d draft(s): draft first (q35_mtp_draft / q35_mtp_draft_k)", k, m->drafts_pending);
     m->drafts_pending = 0;
-    verify_ids_kernel<<<(L * (k + 1) + 255) / 256, 256, 0, st>>>(cur, cand, k, e->tok2, L);
-    CK(cudaGetLastError());
+    CK(launch_k(verify_ids_kernel, dim3((L * (k + 1) + 255) / 256), dim3(256), 0, st, cur, cand, k, e->tok2, L));
     int rc = run_body(e, s, e->tok2, k + 1, k, st);
     if (rc != Q35_OK) return rc;
     rc = run_head(e, e->normed, (k + 1) * L, e->tgt, nullptr, st);
     if (rc != Q35_OK) return rc;
-    mtp_verdict_kernel<<<(L + 7) / 8, 256, 0, st>>>(cand, e->tgt, e->normed, k, emit, n_emit, h_next,
-                                                    s->pos, s->sel, m->n, L);
-    CK(cudaGetLastError());
+    CK(launch_k(mtp_verdict_kernel, dim3((L + 7) / 8), dim3(256), 0, st, cand, e->tgt, e->normed, k, emit, n_emit, h_next,
+                s->pos, s->sel, m->n, L));
     e->n_launch += 2;                             // the id-gather ahead of the body and the verdict
     s->host_pos_hi += k + 1;   // upper bound: lanes that rejected sit lower
     return Q35_OK;

@@ -438,6 +438,7 @@ __global__ void __launch_bounds__(256)
 argmax_final_kernel(const ArgMax* __restrict__ partials, int n_parts, int* __restrict__ tokens,
                     float* __restrict__ top_logit) {
     pdl_wait();
+    pdl_trigger();
     const int row = blockIdx.x;
     const ArgMax* p = partials + (size_t)row * n_parts;
     float bv = -INFINITY;

@@ -52,6 +52,7 @@ add_norm_kernel(const uint16_t* __restrict__ x, const int* __restrict__ ids,
 #pragma unroll
     for (int c = 0; c < 4; ++c) wv[c] = *reinterpret_cast<const uint4*>(w + c * 256 + lane * 8);
     pdl_wait();
+    pdl_trigger();          // the projection behind this kernel may start fetching its weights
     if (row >= rows) return;
     const uint16_t* src;
     if (ids != nullptr) {
@@ -134,6 +135,7 @@ add_norm_split_kernel(const uint16_t* __restrict__ x, const float* __restrict__ 
     const int off = tid * 8;
     const uint4 wv = *reinterpret_cast<const uint4*>(w + off);      // ahead of the wait: weights are immutable
     pdl_wait();
+    pdl_trigger();          // the projection behind this kernel may start fetching its weights
     const uint4 a = *reinterpret_cast<const uint4*>(x + (size_t)row * kHidden + off);
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     const float* pp = parts + (size_t)row * kHidden + off;
@@ -268,6 +270,7 @@ __global__ void fill_int_kernel(int* p, int v, int n) {
 }
 __global__ void add_int_kernel(int* p, int v, int n) {
     pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] += v;
 }
