@@ -523,6 +523,7 @@ def test_attn_prompt_body_vs_oracle(eng, weights, ctxs, T):
     [1100, 2047, 2990, 1024],                                   # capacity 3,008, 4 lanes: clusters of 8 CTAs
     [1024 + (37 * i) % 1900 for i in range(20)],                # 20 lanes: clusters of 4 CTAs
     [1030 + (53 * i) % 1500 for i in range(34)],                # 34 lanes: one CTA per (lane, kv head), alone on its SM
+    [(131 * i) % 1400 for i in range(100)],                     # 100 lanes: 200 CTAs, empty and page-edge contexts
 ])
 def test_attn_long_context_form(eng, weights, ctxs):
     """Contexts beyond 1,024 positions: the TMA forms up to a capacity of 3,072 positions, the
@@ -585,19 +586,21 @@ def test_attn_golden(eng, weights, golden):
     assert rel_l2(mix.float().cpu(), g["mix_q"]) <= 1e-2
 
 
-def test_attn_multi_row_body(eng, weights):
-    """T = 3 new rows per lane in one call (append-all-then-score) equals three single-row calls."""
+@pytest.mark.parametrize("T", [3, 6, 11])
+def test_attn_multi_row_body(eng, weights, T):
+    """T new rows per lane in one call (append-all-then-score) equals T single-row calls: T = 3 takes the
+    cluster form, 6 and 11 one CTA per (row, kv head) (more rows than a cluster serves, fewer than a prompt block)."""
     l = 7
     pre = f"{O.LM}layers.{l}.self_attn."
     gen = torch.Generator().manual_seed(9)
     kv = {}
     O.attn_mixer(weights, pre, torch.randn((10, 1024), generator=gen).to(torch.bfloat16), 0, kv, True)
-    h = torch.randn((3, 1024), generator=gen).to(torch.bfloat16)
+    h = torch.randn((T, 1024), generator=gen).to(torch.bfloat16)
     d = {}
     K0, V0 = torch.cat(kv["k"], 0), torch.cat(kv["v"], 0)
     O.attn_mixer(weights, pre, h, 10, kv, True, d)
-    proj = torch.cat([d["qg"].reshape(3, -1), d["k_raw"].reshape(3, -1), d["v_raw"].reshape(3, -1)], -1)
+    proj = torch.cat([d["qg"].reshape(T, -1), d["k_raw"].reshape(T, -1), d["v_raw"].reshape(T, -1)], -1)
     kpool, vpool, table = paged([K0], [V0], 1, 1)
     out = eng.op_attn_decode(cu(proj), cu(weights[pre + "q_norm.weight"]), cu(weights[pre + "k_norm.weight"]),
-                             cu(kpool), cu(vpool), cu(table), cu(torch.tensor([10], dtype=torch.int32)), 1, T=3)
+                             cu(kpool), cu(vpool), cu(table), cu(torch.tensor([10], dtype=torch.int32)), 1, T=T)
     assert rel_l2(out.float().cpu(), d["gated"].float()) <= 1e-2
