@@ -882,7 +882,7 @@ bool use_persist(int rows, int N) {
 
 }  // namespace
 
-bool linear_tc_eligible(int rows, int N, int K) { return rows > 16 && N >= 128 && K % BK == 0; }   // rows below a tile are zero-filled by TMA
+bool linear_tc_eligible(int rows, int N, int K) { return rows > 16 && N >= 128 && K % BK == 0; }   // fewer rows than a tile: the x box stops at the body's last row
 
 // K splits the tcgen05 form would use for a plain projection (1 = no split).
 int linear_tc_splits(int rows, int N, int K, int max_rows_ws) {
